@@ -12,7 +12,7 @@
 //              tcgen05.commit frees the stage / publishes the accumulator
 //   warps 2-5: epilogue - tcgen05.ld 32 lanes x 16 columns, convert, 16-byte stores
 // All role loops are executed by the whole warp with one elected lane issuing, which keeps the
-// TMA / UMMA operands in uniform registers (back-to-back UTMALDG / UTCHMMA in SASS).
+// TMA / UMMA operands in uniform registers.
 // Split-K: each split writes its fp32 partial tile to a workspace; the CTA that takes the last
 // ticket (acq_rel atomic) sums the partials in split order (deterministic, coalesced).
 // Rows >= M and columns >= N of edge tiles are zero-filled by TMA and masked at the store.
