@@ -277,6 +277,64 @@ int nvc_silu_and_mul(nvc_ctx* ctx, const nvc_bf16* x, nvc_bf16* out, int N, int 
 int nvc_gather_rows(nvc_ctx* ctx, const nvc_bf16* x, const float* residual, const int32_t* rows,
                     nvc_bf16* x_out, float* residual_out, int B, int H, void* stream);
 
+/* ---- mechanisms of the models with an fp32 residual stream (Karuzen).  `dtype` arguments are NVC_DT_BF16 (serving:
+ * bf16 storage, fp32 arithmetic) or NVC_DT_F32 (exact mode: fp32 storage, plain IEEE products and sums); strides are in
+ * elements; buffers may be wider than the logical row (padding columns are never written). ---- */
+enum { NVC_ACT_NONE = 0, NVC_ACT_RELU2 = 1, NVC_ACT_GELU_TANH_MUL = 2 };
+
+/* out[n, :H] = f32(table[ids[n], :H]). */
+int nvc_embed_gather_f32(nvc_ctx* ctx, const int32_t* ids, const void* table, int table_dtype, int ldt, float* out, int ldo,
+                         int N, int H, void* stream);
+/* Dynamic Tanh norm fused with the residual accumulation (all sums fp32):
+ *   s = res_in[r] + a0[r] + a1[r] + a2[r]   (each operand optional, fp32 [*, ld]);  res_out[r] = s (optional, may alias);
+ *   out[i, j] = tanh(alpha * s_j) * w_j + b_j,  j < H     (w == NULL: accumulate only, out must be NULL).
+ * rows == NULL: r = i; else r = rows[i] (gathers N rows; res_out must be NULL).  w, b: fp32 [H]; alpha: fp32 scalar in
+ * device memory. */
+int nvc_dyt_norm(nvc_ctx* ctx, const float* res_in, const float* a0, const float* a1, const float* a2, float* res_out, int ld,
+                 const float* w, const float* b, const float* alpha, void* out, int out_dtype, int ldo, const int32_t* rows,
+                 int N, int H, void* stream);
+/* The two latents of latent attention from one fused down-projection row in[n] (fp32):
+ *   out0[n, :n0]               = rmsnorm(in[n, :n0]) * w0          (query latent)
+ *   cache[slot_mapping[n], :n1] = rmsnorm(in[n, off1 : off1 + n1]) * w1   (key / value latent; slot < 0 skips)
+ * rmsnorm(x) = x / sqrt(mean(x^2) + eps) over the logical width.  cache may be NULL. */
+int nvc_latent_norm_store(nvc_ctx* ctx, const float* in, int ldi, int n0, int off1, int n1, const float* w0, const float* w1,
+                          float eps, void* out0, int ld0, void* cache, int ldc, const int32_t* slot_mapping, int dtype, int N,
+                          void* stream);
+/* kind NVC_ACT_GELU_TANH_MUL: out[n, j] = gelu_tanh(in[n, j]) * in[n, Fp + j];  NVC_ACT_RELU2: out[n, j] = max(in[n, j], 0)^2;
+ * j < F.  in and out may alias for NVC_ACT_RELU2. */
+int nvc_act_mul(nvc_ctx* ctx, const void* in, int ldi, void* out, int ldo, int dtype, int N, int F, int Fp, int kind, void* stream);
+/* C[b] = act(A[b] . W[b]^T) on the fp32 FMA pipe, any sizes: A [M, K] (+ b * sa), W [N, K] (+ b * sw), C [M, N] (+ b * sc),
+ * b < batch.  in_dtype: A and W; out_dtype: C (fp32 operands give fp32).  act: NVC_ACT_NONE or NVC_ACT_RELU2. */
+int nvc_linear(nvc_ctx* ctx, const void* A, int lda, int64_t sa, const void* W, int ldw, int64_t sw, void* C, int ldc, int64_t sc,
+               int in_dtype, int out_dtype, int M, int N, int K, int batch, int act, void* stream);
+/* Grouped form: rows [offsets[g], offsets[g + 1]) of C are act(A[a_rows[r]] . (W + g * sw)^T); offsets: int32 [groups + 1] in
+ * DEVICE memory, offsets[groups] <= max_rows; a_rows may be NULL (identity). */
+int nvc_linear_grouped(nvc_ctx* ctx, const void* A, int lda, const int32_t* a_rows, const void* W, int ldw, int64_t sw, void* C,
+                       int ldc, const int32_t* offsets, int groups, int max_rows, int in_dtype, int out_dtype, int N, int K, int act,
+                       void* stream);
+/* Router of a mixture of experts, one token per warp, fp32: z = W_router h; s = sigmoid(z); the `top` experts with the
+ * largest s + correction (ties -> lower index) are chosen; topk_w = s_chosen / (sum of the chosen s + 1e-20) * scale.
+ * gate[n] = sigmoid(w_shared_gate . h[n]) when w_shared_gate != NULL.  experts <= 256. */
+int nvc_moe_route(nvc_ctx* ctx, const void* h, int h_dtype, int ldh, const float* w_router, const float* correction,
+                  const float* w_shared_gate, int E, int top, float scale, int32_t* topk_idx, float* topk_w, float* gate, int N,
+                  int H, void* stream);
+/* Stable counting sort of the N * top (token, choice) pairs by expert: offsets [E + 1], src_rows [N * top] (token of the
+ * pair at each sorted position), pos [N * top] (sorted position of pair n * top + t). */
+int nvc_moe_sort(nvc_ctx* ctx, const int32_t* topk_idx, int N, int top, int E, int32_t* offsets, int32_t* src_rows, int32_t* pos,
+                 void* stream);
+/* out[n, :H] = sum_t topk_w[n, t] * y[pos[n * top + t], :H] + gate[n] * shared[n, :H]   (fp32; shared / gate optional). */
+int nvc_moe_combine(nvc_ctx* ctx, const void* y, int y_dtype, int ldy, const int32_t* pos, const float* topk_w, int top,
+                    const void* shared, int shared_dtype, int lds, const float* gate, float* out, int ldo, int N, int H,
+                    void* stream);
+/* Latent attention over a paged cache of shared latent rows (absorbed multi-head latent attention, no positional part):
+ *   out[i, h, :D] = sum_{j <= pos_i} softmax_j(scale * q[i, h, :D] . c_j) * c_j,   c_j = cache[slot of token j, :D].
+ * q / out: [rows, heads, head_stride] with row strides ldq / ldo; sequence b owns rows cu_seqlens[b] .. cu_seqlens[b + 1]
+ * (cu_seqlens == NULL: one row per sequence), which are the LAST positions of its context_lens[b] tokens; the slot of token
+ * j is block_tables[b, j / block_size] * block_size + j % block_size.  D <= 512. */
+int nvc_latent_attn_paged(nvc_ctx* ctx, const void* q, int ldq, const void* cache, int ldc, const int32_t* block_tables,
+                          int bt_stride, const int32_t* context_lens, const int32_t* cu_seqlens, int B, int max_qlen, int heads,
+                          int D, int head_stride, int block_size, float scale, void* out, int ldo, int dtype, void* stream);
+
 /* K8. Replaces Qwen3ModelRunner::argmax (src/engine/llm_engine.rs:135-142) on device:
  * idx[b] = LAST index of the maximum of logits[b, :] (Iterator::max_by tie rule);
  * val[b] = that maximum.  idx is offset by `index_offset` (TP vocab shard). */

@@ -46,7 +46,9 @@ typedef struct nvc_runner_options {
   int32_t max_model_len;           /* longest sequence (rope table / block table width)                      */
   int32_t use_cuda_graph;          /* capture decode steps per batch size                                    */
   int32_t allreduce_f32;           /* TP: reduce fp32 partials instead of bf16 (default 0)                   */
-  int32_t reserved[4];
+  int32_t dtype;                   /* registry models: NVC_DT_BF16 (0, serving) or NVC_DT_F32 (exact mode)   */
+  int32_t max_logit_rows;          /* most rows nvc_runner_set_logit_rows may arm (0 = max_num_seqs)         */
+  int32_t reserved[2];
 } nvc_runner_options;
 
 /* ------------------------------------------------------------------ runner */
@@ -65,6 +67,40 @@ int nvc_runner_destroy(nvc_runner* r);
 int nvc_runner_load_weight(nvc_runner* r, const char* hf_name, const nvc_bf16* data, int64_t rows, int64_t cols);
 /* Verifies every tensor arrived, builds the rope table.  Must be called before any step. */
 int nvc_runner_finalize(nvc_runner* r);
+
+/* ---- model registry: any registered architecture from its config.json ----
+ * The architecture is config.json's "architecture" (or the first of HF's "architectures"): "Qwen3ForCausalLM" (the
+ * built-in body above) or "Karuzen" (parallel layers with a Dynamic-Tanh norm, latent attention, dense or
+ * mixture-of-experts feed-forward, a looped block of layers; fp32 residual stream).  Error text:
+ * nvc_model_config_last_error (thread-local). */
+typedef struct nvc_model_config nvc_model_config;
+const char* nvc_model_config_last_error(void);
+int nvc_model_config_load(const char* model_dir, nvc_model_config** out);
+int nvc_model_config_from_json(const char* json_text, nvc_model_config** out);
+void nvc_model_config_free(nvc_model_config* c);
+const char* nvc_model_config_architecture(const nvc_model_config* c);
+int nvc_model_config_vocab(const nvc_model_config* c);
+int nvc_model_config_qwen3(const nvc_model_config* c, nvc_qwen3_config* out, int* tie_word_embeddings);
+/* A runner for the configured architecture (Qwen3: same as nvc_runner_create).  opt->dtype selects the storage format
+ * of a registry model; its steps attend through the paged cache, so they take block_tables (nvc_runner_prefill_paged,
+ * nvc_runner_step_mixed, nvc_runner_decode). */
+int nvc_runner_create_from_config(nvc_ctx* ctx, const nvc_model_config* cfg, const nvc_runner_options* opt, nvc_runner** out);
+/* One checkpoint tensor under its own name, dtype (NVC_ST_*) and shape, host memory (registry models;
+ * nvc_runner_load_hf_dir uses it for them).  1 when the runner takes tensors this way. */
+int nvc_runner_load_tensor(nvc_runner* r, const char* name, const void* data, int st_dtype, const int64_t* shape, int ndim);
+int nvc_runner_takes_raw_tensors(const nvc_runner* r);
+/* 1 when every step of the runner attends through the paged cache (the engine then never calls nvc_runner_prefill). */
+int nvc_runner_needs_block_tables(const nvc_runner* r);
+int nvc_runner_vocab(const nvc_runner* r);
+/* Arms the NEXT prefill / mixed step to compute logits for `n` given rows of its flat token list (instead of the last
+ * row of every sequence); nvc_runner_last_logits then returns [n, vocab].  Such a step samples nothing (out_tokens = -1).
+ * n <= max_logit_rows.  rows == NULL disarms. */
+int nvc_runner_set_logit_rows(nvc_runner* r, const int32_t* rows, int n);
+/* Debug tap: the next step copies the fp32 residual stream after every layer run into host memory,
+ * [layer runs, N, width]; host == NULL disarms. */
+int nvc_runner_set_residual_tap(nvc_runner* r, float* host, int64_t capacity_floats);
+int nvc_runner_layer_runs(const nvc_runner* r);
+int nvc_runner_width(const nvc_runner* r);
 
 /* ---- native HF checkpoint loading (host side; error text in nvc_hf_last_error, thread-local) ---- */
 const char* nvc_hf_last_error(void);
@@ -222,6 +258,21 @@ int nvc_engine_step_emit_mask(const nvc_engine* e, const int32_t** emit);
 int nvc_engine_post_process(nvc_engine* e, const int32_t* token_ids, int n);
 /* LLMEngine::step (:239-264): schedule -> runner -> post_process. */
 int nvc_engine_step(nvc_engine* e, nvc_step_output* out);
+/* Caller-driven requests: the caller, not the scheduler, decides which tokens each step computes (trace replay, a
+ * prefill whose prompt arrives in portions).  They live beside the scheduler's queues and share its block manager and the
+ * runner's cache; they need enable_chunked_prefill.
+ *   open_request: a live request without tokens; returns its seq_id.
+ *   step_forced: ONE step over exactly the n given requests: request i gets counts[i] >= 1 more tokens (tokens: flat, in entry
+ *     order), which are appended to it and computed on top of what it has in the cache; blocks are taken as the request
+ *     grows (NVC_ENOMEM, nothing changed, when the pool cannot hold the step).  One-token continuations are batched first
+ *     and run through the decode attention path, the others as prompt portions.  want_counts[i] offsets of want_offsets
+ *     (flat; each in [0, counts[i])) name the positions whose logits are computed: nvc_runner_last_logits then returns them
+ *     in entry order.  Nothing is sampled and no request ends.
+ *   close_request: gives the request's blocks back. */
+int64_t nvc_engine_open_request(nvc_engine* e);
+int nvc_engine_step_forced(nvc_engine* e, int n, const int64_t* seq_ids, const int32_t* counts, const int32_t* tokens,
+                           const int32_t* want_counts, const int32_t* want_offsets, nvc_step_output* out);
+int nvc_engine_close_request(nvc_engine* e, int64_t seq_id);
 int nvc_engine_is_finished(const nvc_engine* e);
 /* enabled != 0: every nvc_engine_step samples with each sequence's SamplingParams.temperature
  * (sampling_params.rs:6) on device, noise stream = (seq_id << 32 | completion tokens so far), so

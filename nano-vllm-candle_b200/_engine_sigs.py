@@ -16,7 +16,7 @@ class Qwen3ConfigC(C.Structure):
 class RunnerOptionsC(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("num_kvcache_blocks", "kvcache_block_size", "max_num_seqs",
                                          "max_num_batched_tokens", "max_model_len", "use_cuda_graph",
-                                         "allreduce_f32")] + [("reserved", C.c_int32 * 4)]
+                                         "allreduce_f32", "dtype", "max_logit_rows")] + [("reserved", C.c_int32 * 2)]
 
 
 class SchedulerConfigC(C.Structure):
@@ -59,6 +59,21 @@ def declare(l: C.CDLL) -> None:
         "nvc_runner_time_decode": [_vp, _i, C.POINTER(C.c_float), C.POINTER(C.c_int)],
         "nvc_runner_time_op": [_vp, _i, _i, C.POINTER(C.c_float), C.POINTER(C.c_int)],
         "nvc_runner_get_options": [_vp, C.POINTER(RunnerOptionsC)],
+        "nvc_model_config_load": [C.c_char_p, C.POINTER(_vp)],
+        "nvc_model_config_from_json": [C.c_char_p, C.POINTER(_vp)],
+        "nvc_model_config_vocab": [_vp],
+        "nvc_model_config_qwen3": [_vp, C.POINTER(Qwen3ConfigC), C.POINTER(C.c_int)],
+        "nvc_runner_create_from_config": [_vp, _vp, C.POINTER(RunnerOptionsC), C.POINTER(_vp)],
+        "nvc_runner_load_tensor": [_vp, C.c_char_p, _vp, _i, C.POINTER(C.c_int64), _i],
+        "nvc_runner_takes_raw_tensors": [_vp],
+        "nvc_runner_needs_block_tables": [_vp],
+        "nvc_runner_vocab": [_vp],
+        "nvc_runner_set_logit_rows": [_vp, _vp, _i],
+        "nvc_runner_set_residual_tap": [_vp, _vp, _i64],
+        "nvc_runner_layer_runs": [_vp],
+        "nvc_runner_width": [_vp],
+        "nvc_engine_step_forced": [_vp, _i, _vp, _vp, _vp, _vp, _vp, C.POINTER(StepOutputC)],
+        "nvc_engine_close_request": [_vp, _i64],
         "nvc_engine_create": [C.POINTER(SchedulerConfigC), _vp, C.POINTER(_vp)],
         "nvc_engine_destroy": [_vp],
         "nvc_engine_schedule": [_vp, C.POINTER(ScheduleInfoC)],
@@ -83,6 +98,14 @@ def declare(l: C.CDLL) -> None:
         fn.restype = _i
     l.nvc_engine_add_request.argtypes = [_vp, _vp, _i, C.c_double, _i, _i]
     l.nvc_engine_add_request.restype = _i64
+    l.nvc_engine_open_request.argtypes = [_vp]
+    l.nvc_engine_open_request.restype = _i64
+    l.nvc_model_config_free.argtypes = [_vp]
+    l.nvc_model_config_free.restype = None
+    l.nvc_model_config_architecture.argtypes = [_vp]
+    l.nvc_model_config_architecture.restype = C.c_char_p
+    l.nvc_model_config_last_error.argtypes = []
+    l.nvc_model_config_last_error.restype = C.c_char_p
     l.nvc_hf_last_error.argtypes = []
     l.nvc_hf_last_error.restype = C.c_char_p
     l.nvc_hf_last_warning.argtypes = []

@@ -91,6 +91,16 @@ def _declare(l: C.CDLL) -> None:
         "nvc_gather_rows": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
         "nvc_argmax_last": [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _vp],
         "nvc_sample_gumbel": [_vp, _vp, _i, _vp, _vp, C.c_uint64, _vp, _vp, _i, _i, _i, _vp],
+        "nvc_embed_gather_f32": [_vp, _vp, _vp, _i, _i, _vp, _i, _i, _i, _vp],
+        "nvc_dyt_norm": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _vp, _i, _i, _vp],
+        "nvc_latent_norm_store": [_vp, _vp, _i, _i, _i, _i, _vp, _vp, _f, _vp, _i, _vp, _i, _vp, _i, _i, _vp],
+        "nvc_act_mul": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _vp],
+        "nvc_linear": [_vp, _vp, _i, C.c_int64, _vp, _i, C.c_int64, _vp, _i, C.c_int64, _i, _i, _i, _i, _i, _i, _i, _vp],
+        "nvc_linear_grouped": [_vp, _vp, _i, _vp, _vp, _i, C.c_int64, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+        "nvc_moe_route": [_vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _f, _vp, _vp, _vp, _i, _i, _vp],
+        "nvc_moe_sort": [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp],
+        "nvc_moe_combine": [_vp, _vp, _i, _i, _vp, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _vp],
+        "nvc_latent_attn_paged": [_vp, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _i, _i, _vp],
         "nvc_debug_set": [_i, _i],
     }
     for name, args in sigs.items():

@@ -211,6 +211,15 @@ struct BlockManager {
       b.token_ids.clear();
     }
   }
+  // Caller-driven sequences (nvc_engine_step_forced) grow by whole portions: blocks up to `nb` in total.
+  size_t blocks_missing(const Sequence& s, size_t nb) const { return nb > s.block_table.size() ? nb - s.block_table.size() : 0; }
+  void grow(Sequence& s, size_t nb) {
+    while (s.block_table.size() < nb) {
+      const int32_t id = free_.front();
+      take(id);
+      s.block_table.push_back(id);
+    }
+  }
   bool can_append(const Sequence& s) const {
     // a block is missing only when the newest token opens one (len % block_size == 1) and the table
     // does not hold it yet (it does when that token is still part of the prompt: chunked prefill)
@@ -709,6 +718,7 @@ int nvc_engine_step(nvc_engine* e, nvc_step_output* out) {
   } else if (e->batch_is_prefill) {
     bool cached_prefix = false;   // some sequence skips a cached prefix: attention must read it from the paged cache
     for (auto& s : e->batch) cached_prefix |= s->num_cached_tokens > 0;
+    cached_prefix |= nvc_runner_needs_block_tables(e->runner) != 0;
     if (cached_prefix)
       rc = nvc_runner_prefill_paged(e->runner, e->ids.data(), e->positions.data(), e->cu_seqlens.data(),
                                     e->slot_mapping.data(), e->block_tables.data(), e->max_blocks, e->context_lens.data(),
@@ -748,6 +758,165 @@ int nvc_engine_step(nvc_engine* e, nvc_step_output* out) {
     out->num_tokens = tot;
   } else {
     out->num_tokens = -B;
+  }
+  return NVC_OK;
+}
+
+// ---- caller-driven sequences: the caller, not the scheduler, says which tokens every step computes ----
+int64_t nvc_engine_open_request(nvc_engine* e) {
+  if (!e) return NVC_EINVAL;
+  if (!e->chunked) {
+    e->err = "caller-driven requests need chunked prefill (mixed steps)";
+    return NVC_ESTATE;
+  }
+  auto s = std::make_shared<Sequence>();
+  s->seq_id = e->next_seq_id++;
+  s->block_size = e->block_size;
+  s->status = Status::Running;       // lives outside the scheduler's queues
+  s->max_tokens = 0;
+  e->all[s->seq_id] = s;
+  return s->seq_id;
+}
+
+int nvc_engine_close_request(nvc_engine* e, int64_t seq_id) {
+  if (!e) return NVC_EINVAL;
+  auto it = e->all.find(seq_id);
+  if (it == e->all.end() || it->second->max_tokens != 0 || it->second->is_finished()) {
+    e->err = "close_request: not an open caller-driven request";
+    return NVC_EINVAL;
+  }
+  e->scheduler.block_manager.deallocate(*it->second);
+  it->second->status = Status::Finished;
+  e->all.erase(it);
+  e->batch_valid = false;
+  return NVC_OK;
+}
+
+int nvc_engine_step_forced(nvc_engine* e, int n, const int64_t* seq_ids, const int32_t* counts, const int32_t* tokens,
+                           const int32_t* want_counts, const int32_t* want_offsets, nvc_step_output* out) {
+  if (!e || !seq_ids || !counts || !tokens || n <= 0) return NVC_EINVAL;
+  if (!e->chunked || !e->runner) {
+    e->err = "step_forced needs chunked prefill and a model runner";
+    return NVC_ESTATE;
+  }
+  BlockManager& bm = e->scheduler.block_manager;
+  const size_t bs = (size_t)e->block_size;
+  std::vector<SeqPtr> seqs;
+  size_t missing = 0, total = 0;
+  for (int i = 0; i < n; ++i) {
+    auto it = e->all.find(seq_ids[i]);
+    if (it == e->all.end() || it->second->max_tokens != 0 || it->second->is_finished() || counts[i] <= 0) {
+      e->err = "step_forced: entry " + std::to_string(i) + " is not an open caller-driven request with tokens";
+      return NVC_EINVAL;
+    }
+    for (auto& p : seqs)
+      if (p == it->second) { e->err = "step_forced: a request appears twice"; return NVC_EINVAL; }
+    const Sequence& sq = *it->second;
+    const size_t len = sq.len() + (size_t)counts[i];
+    if (e->scheduler.max_model_len > 0 && len > e->scheduler.max_model_len) {
+      e->err = "step_forced: request grows past max_model_len";
+      return NVC_EINVAL;
+    }
+    missing += bm.blocks_missing(sq, (len + bs - 1) / bs);
+    total += (size_t)counts[i];
+    seqs.push_back(it->second);
+  }
+  if ((size_t)n > e->scheduler.max_num_seqs || total > e->scheduler.max_num_batched_tokens) {
+    e->err = "step_forced: the step exceeds max_num_seqs / max_num_batched_tokens";
+    return NVC_ENOMEM;
+  }
+  if (missing > bm.free_.size()) {
+    e->err = "step_forced: KV pool exhausted";
+    return NVC_ENOMEM;
+  }
+  // append the portions, grow the block tables; one-token continuations lead the batch (paged decode kernels)
+  std::vector<int> order;
+  {
+    size_t off = 0;
+    for (int i = 0; i < n; ++i) {
+      Sequence& sq = *seqs[i];
+      for (int t = 0; t < counts[i]; ++t) sq.append_token(tokens[off + t]);
+      sq.num_prompt_tokens = sq.num_tokens;
+      off += (size_t)counts[i];
+      bm.grow(sq, sq.num_blocks());
+    }
+    for (int i = 0; i < n; ++i)
+      if (counts[i] == 1 && seqs[i]->num_computed_tokens > 0) order.push_back(i);
+    e->num_decode = (int)order.size();
+    for (int i = 0; i < n; ++i)
+      if (!(counts[i] == 1 && seqs[i]->num_computed_tokens > 0)) order.push_back(i);
+  }
+  e->batch.clear();
+  e->q_lens.clear();
+  std::vector<int> place(n);
+  for (int k = 0; k < n; ++k) {
+    e->batch.push_back(seqs[order[k]]);
+    e->q_lens.push_back(counts[order[k]]);
+    place[order[k]] = k;
+  }
+  e->batch_is_prefill = e->num_decode < n;
+  build_inputs(e);
+  e->batch_valid = true;
+  std::vector<int32_t> rows;
+  if (want_counts && want_offsets) {
+    size_t off = 0;
+    for (int i = 0; i < n; ++i) {
+      for (int k = 0; k < want_counts[i]; ++k) {
+        const int32_t o = want_offsets[off + k];
+        if (o < 0 || o >= counts[i]) { e->err = "step_forced: wanted offset outside the portion"; rows.clear(); off = (size_t)-1; break; }
+        rows.push_back(e->cu_seqlens[place[i]] + o);
+      }
+      if (off == (size_t)-1) break;
+      off += (size_t)want_counts[i];
+    }
+    if (off == (size_t)-1) {
+      for (int i = 0; i < n; ++i) {     // undo the append
+        Sequence& sq = *seqs[i];
+        sq.token_ids.resize(sq.token_ids.size() - (size_t)counts[i]);
+        sq.num_tokens -= (size_t)counts[i];
+        sq.num_prompt_tokens = sq.num_tokens;
+        sq.last_token = sq.token_ids.empty() ? 0 : sq.token_ids.back();
+      }
+      e->batch_valid = false;
+      return NVC_EINVAL;
+    }
+  }
+  const int B = n;
+  e->out_tokens.assign(B, 0);
+  int rc = NVC_OK;
+  if (!rows.empty()) rc = nvc_runner_set_logit_rows(e->runner, rows.data(), (int)rows.size());
+  if (rc == NVC_OK) {
+    if (rows.empty() && e->num_decode == B)
+      rc = nvc_runner_decode(e->runner, e->ids.data(), e->positions.data(), e->slot_mapping.data(), e->block_tables.data(),
+                             e->max_blocks, e->context_lens.data(), B, e->out_tokens.data());
+    else
+      rc = nvc_runner_step_mixed(e->runner, e->ids.data(), e->positions.data(), e->cu_seqlens.data(), e->slot_mapping.data(),
+                                 e->block_tables.data(), e->max_blocks, e->context_lens.data(), e->num_decode, B, (int)e->ids.size(),
+                                 e->max_seqlen, e->out_tokens.data());
+  }
+  if (rc) {
+    nvc_runner_set_logit_rows(e->runner, nullptr, 0);
+    for (int i = 0; i < n; ++i) {       // the portions were not computed: take them back (grown blocks stay with the request)
+      Sequence& sq = *seqs[i];
+      sq.token_ids.resize(sq.token_ids.size() - (size_t)counts[i]);
+      sq.num_tokens -= (size_t)counts[i];
+      sq.num_prompt_tokens = sq.num_tokens;
+      sq.last_token = sq.token_ids.empty() ? 0 : sq.token_ids.back();
+    }
+    e->batch_valid = false;
+    e->err = "step_forced: runner step failed";
+    return rc;
+  }
+  for (int k = 0; k < B; ++k) e->scheduler.mark_computed(e->batch[k], (size_t)e->q_lens[k]);
+  e->batch_valid = false;
+  if (out) {
+    out->is_prefill = e->batch_is_prefill;
+    out->num_tokens = (int)e->ids.size();
+    out->num_seqs = B;
+    out->num_finished = 0;
+    out->num_query_tokens = (int)e->ids.size();
+    out->num_sampled = 0;
+    out->num_decode_seqs = e->num_decode;
   }
   return NVC_OK;
 }

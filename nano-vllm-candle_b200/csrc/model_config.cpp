@@ -1,0 +1,170 @@
+// Model registry, configuration side: config.json -> nvc_model_config.  The architecture is taken from config.json
+// ("architecture": "<name>", or the first entry of HF's "architectures" list); each registered family parses its own keys.
+// Plain host C++ (also built without CUDA by the sanitizer tests).
+#include "model_config.h"
+
+#include "json.h"
+
+using namespace nvcjson;
+
+namespace {
+
+thread_local std::string g_cfg_error;
+
+int cfg_fail(const std::string& m) {
+  g_cfg_error = m;
+  return NVC_EINVAL;
+}
+
+bool get_int(const JValue* o, const char* key, int& out, int lo, std::string& err) {
+  const JValue* v = o ? o->get(key) : nullptr;
+  if (!v || v->kind != JValue::Num || v->num != (double)(int64_t)v->num || v->num < lo || v->num > 2147483647.0) {
+    err = std::string("missing or invalid integer `") + key + "`";
+    return false;
+  }
+  out = (int)v->num;
+  return true;
+}
+bool get_float(const JValue* o, const char* key, float& out, std::string& err) {
+  const JValue* v = o ? o->get(key) : nullptr;
+  if (!v || v->kind != JValue::Num) {
+    err = std::string("missing or invalid number `") + key + "`";
+    return false;
+  }
+  out = (float)v->num;
+  return true;
+}
+
+int parse_karuzen(const JValue& root, nvc_karuzen_config& c) {
+  std::string err;
+  if (!get_int(&root, "vocab", c.vocab, 1, err) || !get_int(&root, "width", c.width, 1, err)) return cfg_fail(err);
+  const JValue* norm = root.get("norm");
+  if (!norm || norm->kind != JValue::Obj || !get_float(norm, "eps", c.eps, err)) return cfg_fail("norm.eps: " + err);
+  const JValue* layers = root.get("layers");
+  if (!layers || layers->kind != JValue::Arr || layers->arr.empty()) return cfg_fail("`layers` must be a non-empty list");
+  for (size_t i = 0; i < layers->arr.size(); ++i) {
+    const JValue& jl = layers->arr[i];
+    const std::string where = "layers[" + std::to_string(i) + "]: ";
+    if (jl.kind != JValue::Obj) return cfg_fail(where + "not an object");
+    nvc_karuzen_layer L;
+    const JValue* type = jl.get("type");
+    if (!type || type->kind != JValue::Str) return cfg_fail(where + "missing `type`");
+    L.mixer.type = type->str;
+    if (L.mixer.type != "latent_attention") return cfg_fail(where + "mixer type `" + L.mixer.type + "` is not supported");
+    const JValue* m = jl.get("mixer");
+    if (!m || m->kind != JValue::Obj) return cfg_fail(where + "missing `mixer`");
+    if (!get_int(m, "heads", L.mixer.heads, 1, err) || !get_int(m, "dim", L.mixer.dim, 1, err) ||
+        !get_int(m, "vdim", L.mixer.vdim, 1, err) || !get_int(m, "kv_rank", L.mixer.kv_rank, 1, err) ||
+        !get_int(m, "q_rank", L.mixer.q_rank, 1, err) || !get_float(m, "scale", L.mixer.scale, err))
+      return cfg_fail(where + "mixer: " + err);
+    const JValue* mlp = jl.get("mlp");
+    if (mlp && mlp->kind == JValue::Obj) {
+      const JValue* kind = mlp->get("kind");
+      if (!kind || kind->kind != JValue::Str) return cfg_fail(where + "mlp: missing `kind`");
+      if (kind->str == "dense") {
+        L.mlp.kind = nvc_karuzen_mlp::Dense;
+        if (!get_int(mlp, "ff", L.mlp.ff, 1, err)) return cfg_fail(where + "mlp: " + err);
+      } else if (kind->str == "moe") {
+        L.mlp.kind = nvc_karuzen_mlp::Moe;
+        const JValue* r = mlp->get("router");
+        const JValue* e = mlp->get("expert");
+        if (!r || !e) return cfg_fail(where + "mlp: a mixture of experts needs `router` and `expert`");
+        if (!get_int(r, "experts", L.mlp.experts, 1, err) || !get_int(r, "top", L.mlp.top, 1, err) ||
+            !get_float(r, "scale", L.mlp.router_scale, err) || !get_int(e, "ff", L.mlp.expert_ff, 1, err))
+          return cfg_fail(where + "mlp: " + err);
+        if (L.mlp.top > L.mlp.experts) return cfg_fail(where + "mlp: top exceeds experts");
+        const JValue* sh = mlp->get("shared");
+        if (sh && sh->kind == JValue::Obj && !get_int(sh, "ff", L.mlp.shared_ff, 1, err)) return cfg_fail(where + "mlp.shared: " + err);
+      } else {
+        return cfg_fail(where + "mlp kind `" + kind->str + "` is not supported");
+      }
+    } else if (mlp && mlp->kind != JValue::Null) {
+      return cfg_fail(where + "`mlp` must be an object or null");
+    }
+    c.layers.push_back(L);
+  }
+  const int n = (int)c.layers.size();
+  c.loop_start = c.loop_stop = 0;
+  c.loop_times = 1;
+  const JValue* loop = root.get("loop");
+  if (loop && loop->kind == JValue::Obj) {
+    if (!get_int(loop, "start", c.loop_start, 0, err) || !get_int(loop, "stop", c.loop_stop, 0, err) ||
+        !get_int(loop, "times", c.loop_times, 1, err))
+      return cfg_fail("loop: " + err);
+    if (c.loop_start > c.loop_stop || c.loop_stop > n) return cfg_fail("loop: start <= stop <= number of layers is required");
+  } else if (loop && loop->kind != JValue::Null) {
+    return cfg_fail("`loop` must be an object or null");
+  }
+  return NVC_OK;
+}
+
+}  // namespace
+
+std::vector<nvc_karuzen_config::Run> nvc_karuzen_config::runs() const {
+  std::vector<Run> out;
+  for (int i = 0; i < loop_start; ++i) out.push_back({i, 0, false});
+  for (int t = 0; t < (loop_stop > loop_start ? loop_times : 0); ++t)
+    for (int i = loop_start; i < loop_stop; ++i) out.push_back({i, t, t > 0 && i == loop_start});
+  for (int i = loop_stop; i < (int)layers.size(); ++i) out.push_back({i, 0, false});
+  return out;
+}
+
+extern "C" {
+
+const char* nvc_model_config_last_error(void) { return g_cfg_error.c_str(); }
+
+int nvc_model_config_from_json(const char* text, nvc_model_config** out) {
+  if (!text || !out) return cfg_fail("null pointer");
+  *out = nullptr;
+  JValue root;
+  std::string err;
+  if (!parse_json(text, strlen(text), root, err) || root.kind != JValue::Obj) return cfg_fail("config is not a JSON object: " + err);
+  std::string arch;
+  if (const JValue* a = root.get("architecture"); a && a->kind == JValue::Str) arch = a->str;
+  if (arch.empty())
+    if (const JValue* a = root.get("architectures"); a && a->kind == JValue::Arr && !a->arr.empty() && a->arr[0].kind == JValue::Str)
+      arch = a->arr[0].str;
+  if (arch.empty())
+    if (const JValue* a = root.get("model_type"); a && a->kind == JValue::Str && a->str == "qwen3") arch = "Qwen3ForCausalLM";
+  auto* c = new nvc_model_config();
+  c->architecture = arch;
+  int rc = NVC_OK;
+  if (arch == "Karuzen") {
+    rc = parse_karuzen(root, c->karuzen);
+  } else if (arch == "Qwen3ForCausalLM") {
+    // parsed by nvc_qwen3_config_from_hf_dir (hf_loader.cpp) when loaded from a directory
+  } else {
+    rc = cfg_fail("architecture `" + arch + "` is not registered (known: Qwen3ForCausalLM, Karuzen)");
+  }
+  if (rc) { delete c; return rc; }
+  *out = c;
+  return NVC_OK;
+}
+
+int nvc_model_config_load(const char* model_dir, nvc_model_config** out) {
+  if (!model_dir || !out) return cfg_fail("null pointer");
+  std::string text;
+  if (!read_file(std::string(model_dir) + "/config.json", text)) return cfg_fail(std::string("cannot read ") + model_dir + "/config.json");
+  int rc = nvc_model_config_from_json(text.c_str(), out);
+  if (rc) return rc;
+  if ((*out)->architecture == "Qwen3ForCausalLM") {
+    rc = nvc_qwen3_config_from_hf_dir(model_dir, &(*out)->qwen3, &(*out)->qwen3_tied);
+    if (rc) { g_cfg_error = nvc_hf_last_error(); delete *out; *out = nullptr; }
+  }
+  return rc;
+}
+
+void nvc_model_config_free(nvc_model_config* c) { delete c; }
+const char* nvc_model_config_architecture(const nvc_model_config* c) { return c ? c->architecture.c_str() : ""; }
+int nvc_model_config_vocab(const nvc_model_config* c) {
+  if (!c) return 0;
+  return c->architecture == "Karuzen" ? c->karuzen.vocab : c->qwen3.vocab_size;
+}
+int nvc_model_config_qwen3(const nvc_model_config* c, nvc_qwen3_config* out, int* tied) {
+  if (!c || !out || c->architecture != "Qwen3ForCausalLM") return NVC_EINVAL;
+  *out = c->qwen3;
+  if (tied) *tied = c->qwen3_tied;
+  return NVC_OK;
+}
+
+}  // extern "C"

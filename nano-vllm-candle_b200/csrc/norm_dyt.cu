@@ -1,0 +1,152 @@
+// Norms and row operations of the models whose residual stream and norms are fp32 end to end:
+//   nvc_embed_gather_f32    token rows of the embedding table as fp32
+//   nvc_dyt_norm            Dynamic Tanh norm (no mean, no variance) fused with the residual accumulation
+//   nvc_latent_norm_store   plain-weight RMS norms of the two low-rank latents of latent attention, the key / value
+//                           latent scattered into the paged cache in the same pass
+//   nvc_act_mul             gated / plain feed-forward activations (tanh-gelu gate, squared relu)
+// Every kernel exists for bf16 and fp32 storage; arithmetic is fp32.
+#include "typed.cuh"
+
+namespace {
+
+template <typename T>
+__global__ void embed_gather_f32_kernel(const int32_t* __restrict__ ids, const T* __restrict__ table, int ldt,
+                                        float* __restrict__ out, int ldo, int N, int H) {
+  pdl_trigger();
+  pdl_wait();
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)N * H) return;
+  const int n = (int)(i / H), j = (int)(i % H);
+  out[(int64_t)n * ldo + j] = ld_f(table + (int64_t)ids[n] * ldt + j);
+}
+
+// one CTA per output row
+template <typename T>
+__global__ void dyt_norm_kernel(const float* __restrict__ res_in, const float* __restrict__ a0, const float* __restrict__ a1,
+                                const float* __restrict__ a2, float* __restrict__ res_out, int ld, const float* __restrict__ w,
+                                const float* __restrict__ b, const float* __restrict__ alpha, T* __restrict__ out, int ldo,
+                                const int32_t* __restrict__ rows, int H) {
+  pdl_trigger();
+  const float al = w ? __ldg(alpha) : 0.f;
+  pdl_wait();
+  const int64_t src = rows ? rows[blockIdx.x] : blockIdx.x;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) {
+    const int64_t k = src * ld + j;
+    float s = res_in ? res_in[k] : 0.f;
+    if (a0) s += a0[k];
+    if (a1) s += a1[k];
+    if (a2) s += a2[k];
+    if (res_out) res_out[k] = s;
+    if (w) st_f(out + (int64_t)blockIdx.x * ldo + j, tanh_f32(al * s) * __ldg(w + j) + __ldg(b + j));
+  }
+}
+
+// one warp per row: segment 0 = columns [0, n0) -> out0; segment 1 = columns [off1, off1 + n1) -> the cache row of the slot
+template <typename T>
+__global__ void latent_norm_store_kernel(const float* __restrict__ in, int ldi, int n0, int off1, int n1,
+                                         const float* __restrict__ w0, const float* __restrict__ w1, float eps,
+                                         T* __restrict__ out0, int ld0, T* __restrict__ cache, int ldc,
+                                         const int32_t* __restrict__ slots, int N) {
+  pdl_trigger();
+  pdl_wait();
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= N) return;
+  const float* x = in + (int64_t)row * ldi;
+  float ss = 0.f;
+  for (int j = lane; j < n0; j += 32) ss += x[j] * x[j];
+  ss = warp_sum(ss);
+  float r = 1.0f / sqrtf(ss / (float)n0 + eps);
+  for (int j = lane; j < n0; j += 32) st_f(out0 + (int64_t)row * ld0 + j, x[j] * r * __ldg(w0 + j));
+  const int slot = slots ? slots[row] : -1;
+  if (slot < 0 || !cache) return;
+  ss = 0.f;
+  for (int j = lane; j < n1; j += 32) ss += x[off1 + j] * x[off1 + j];
+  ss = warp_sum(ss);
+  r = 1.0f / sqrtf(ss / (float)n1 + eps);
+  for (int j = lane; j < n1; j += 32) st_f(cache + (int64_t)slot * ldc + j, x[off1 + j] * r * __ldg(w1 + j));
+}
+
+// NVC_ACT_GELU_TANH_MUL: out[n, j] = gelu_tanh(in[n, j]) * in[n, Fp + j];  NVC_ACT_RELU2: out[n, j] = relu(in[n, j])^2
+template <typename T>
+__global__ void act_mul_kernel(const T* __restrict__ in, int ldi, T* __restrict__ out, int ldo, int N, int F, int Fp, int kind) {
+  pdl_trigger();
+  pdl_wait();
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)N * F) return;
+  const int n = (int)(i / F), j = (int)(i % F);
+  const float g = ld_f(in + (int64_t)n * ldi + j);
+  float y;
+  if (kind == NVC_ACT_GELU_TANH_MUL) {
+    y = gelu_tanh_f32(g) * ld_f(in + (int64_t)n * ldi + Fp + j);
+  } else {
+    const float t = fmaxf(g, 0.f);
+    y = t * t;
+  }
+  st_f(out + (int64_t)n * ldo + j, y);
+}
+
+}  // namespace
+
+extern "C" {
+
+int nvc_embed_gather_f32(nvc_ctx* ctx, const int32_t* ids, const void* table, int table_dtype, int ldt, float* out, int ldo,
+                         int N, int H, void* stream) {
+  NVC_REQUIRE(ctx, ctx && ids && table && out, NVC_EINVAL, "null pointer");
+  NVC_REQUIRE(ctx, N >= 0 && H > 0 && ldt >= H && ldo >= H, NVC_EINVAL, "bad sizes");
+  if (N == 0) return NVC_OK;
+  const int64_t total = (int64_t)N * H;
+  NVC_DISPATCH_DT(table_dtype, T,
+                  NVC_CUDA_CHECK(ctx, nvc_launch(ctx, embed_gather_f32_kernel<T>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0,
+                                                 nvc_stream(stream), ids, reinterpret_cast<const T*>(table), ldt, out, ldo, N, H)));
+  ctx->launches++;
+  return NVC_OK;
+}
+
+int nvc_dyt_norm(nvc_ctx* ctx, const float* res_in, const float* a0, const float* a1, const float* a2, float* res_out, int ld,
+                 const float* w, const float* b, const float* alpha, void* out, int out_dtype, int ldo, const int32_t* rows,
+                 int N, int H, void* stream) {
+  NVC_REQUIRE(ctx, ctx && (res_in || a0), NVC_EINVAL, "null pointer");
+  NVC_REQUIRE(ctx, (w == nullptr) == (out == nullptr) && (!w || (b && alpha)), NVC_EINVAL, "norm needs weight, bias, alpha and an output");
+  NVC_REQUIRE(ctx, N >= 0 && H > 0 && ld >= H && (!w || ldo >= H), NVC_EINVAL, "bad sizes");
+  NVC_REQUIRE(ctx, !(rows && res_out), NVC_EINVAL, "a gathering call does not write the residual back");
+  if (N == 0) return NVC_OK;
+  const int threads = H >= 1024 ? 512 : (H >= 256 ? 256 : 128);
+  NVC_DISPATCH_DT(out_dtype, T,
+                  NVC_CUDA_CHECK(ctx, nvc_launch(ctx, dyt_norm_kernel<T>, dim3(N), dim3(threads), 0, nvc_stream(stream), res_in, a0, a1, a2,
+                                                 res_out, ld, w, b, alpha, reinterpret_cast<T*>(out), ldo, rows, H)));
+  ctx->launches++;
+  return NVC_OK;
+}
+
+int nvc_latent_norm_store(nvc_ctx* ctx, const float* in, int ldi, int n0, int off1, int n1, const float* w0, const float* w1,
+                          float eps, void* out0, int ld0, void* cache, int ldc, const int32_t* slot_mapping, int dtype, int N,
+                          void* stream) {
+  NVC_REQUIRE(ctx, ctx && in && w0 && out0, NVC_EINVAL, "null pointer");
+  NVC_REQUIRE(ctx, !cache || (w1 && slot_mapping), NVC_EINVAL, "a cache needs its norm weight and the slot mapping");
+  NVC_REQUIRE(ctx, N >= 0 && n0 > 0 && n1 >= 0 && off1 >= n0 && ldi >= off1 + n1 && ld0 >= n0 && (!cache || ldc >= n1), NVC_EINVAL,
+              "bad sizes");
+  if (N == 0) return NVC_OK;
+  NVC_DISPATCH_DT(dtype, T,
+                  NVC_CUDA_CHECK(ctx, nvc_launch(ctx, latent_norm_store_kernel<T>, dim3((N + 3) / 4), dim3(128), 0, nvc_stream(stream), in,
+                                                 ldi, n0, off1, n1, w0, w1, eps, reinterpret_cast<T*>(out0), ld0,
+                                                 reinterpret_cast<T*>(cache), ldc, slot_mapping, N)));
+  ctx->launches++;
+  return NVC_OK;
+}
+
+int nvc_act_mul(nvc_ctx* ctx, const void* in, int ldi, void* out, int ldo, int dtype, int N, int F, int Fp, int kind, void* stream) {
+  NVC_REQUIRE(ctx, ctx && in && out, NVC_EINVAL, "null pointer");
+  NVC_REQUIRE(ctx, N >= 0 && F > 0 && (kind == NVC_ACT_GELU_TANH_MUL || kind == NVC_ACT_RELU2), NVC_EINVAL, "bad arguments");
+  NVC_REQUIRE(ctx, ldo >= F && ldi >= (kind == NVC_ACT_GELU_TANH_MUL ? Fp + F : F), NVC_EINVAL, "bad strides");
+  if (N == 0) return NVC_OK;
+  const int64_t total = (int64_t)N * F;
+  NVC_DISPATCH_DT(dtype, T,
+                  NVC_CUDA_CHECK(ctx, nvc_launch(ctx, act_mul_kernel<T>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0,
+                                                 nvc_stream(stream), reinterpret_cast<const T*>(in), ldi, reinterpret_cast<T*>(out), ldo,
+                                                 N, F, Fp, kind)));
+  ctx->launches++;
+  return NVC_OK;
+}
+
+}  // extern "C"

@@ -8,8 +8,8 @@
 //   -> attention -> o_proj GEMM [-> all-reduce]
 //   -> fused_add_rmsnorm -> gate_up GEMM (+ SiLU-mul epilogue) -> down GEMM [-> all-reduce]
 // then: gather last rows -> final fused_add_rmsnorm -> lm_head GEMM (fp32) -> argmax.
-#include "common.cuh"
-#include "internal.h"
+#include "runner.h"
+#include "model_config.h"
 
 #include <algorithm>
 #include <cstdlib>
@@ -18,69 +18,8 @@
 #include <set>
 #include <vector>
 
-namespace {
-
-struct Layer {
-  nvc_bf16 *w_qkv = nullptr, *w_o = nullptr, *q_norm = nullptr, *k_norm = nullptr;
-  nvc_bf16 *w_gu = nullptr, *w_down = nullptr, *ln1 = nullptr, *ln2 = nullptr;
-  nvc_bf16 *k_cache = nullptr, *v_cache = nullptr;
-};
-
-struct ArgPair { float val; int32_t idx; };
-
-}  // namespace
-
-struct nvc_runner {
-  nvc_ctx* ctx = nullptr;
-  nvc_qwen3_config cfg{};
-  nvc_runner_options opt{};
-  int tp = 1, rank = 0;
-  int nh_l = 0, kv_l = 0, I_l = 0, V_l = 0, qkv_l = 0, max_blocks_cap = 0;
-  bool finalized = false;
-  cudaStream_t stream = nullptr;
-  std::vector<Layer> layers;
-  nvc_bf16 *embed = nullptr, *final_norm = nullptr, *lm_head = nullptr;
-  float* rope = nullptr;
-  std::set<std::string> loaded;
-  int64_t weight_bytes = 0;
-  std::vector<void*> allocs;
-  // activations
-  nvc_bf16 *x = nullptr, *xn = nullptr, *qkv = nullptr, *attn = nullptr, *act = nullptr;
-  float* residual = nullptr;
-  nvc_bf16 *x_last = nullptr, *xn_last = nullptr;
-  float *res_last = nullptr, *logits = nullptr;
-  void* decode_ws = nullptr;
-  size_t decode_ws_bytes = 0;
-  // step inputs on device + pinned staging
-  int32_t* d_cu2 = nullptr;     // mixed step: cu_seqlens of the prompt chunks, relative to their first token
-  int32_t *d_ids = nullptr, *d_pos = nullptr, *d_cu = nullptr, *d_slots = nullptr, *d_bt = nullptr, *d_ctx = nullptr,
-          *d_last_rows = nullptr, *d_tok = nullptr;
-  float* d_tok_val = nullptr;
-  ArgPair* d_pairs = nullptr;
-  int32_t* h_stage = nullptr;   // pinned
-  size_t h_stage_ints = 0;
-  size_t in_pitch = 0;             // ints between d_ids / d_pos / d_slots / d_ctx (one block: a decode step uploads all four in ONE 2-D copy)
-  std::vector<int32_t> bt_mirror;  // the padded block table the device holds (decode steps re-upload it only when it changed)
-  int bt_mirror_B = -1;            // rows of bt_mirror that are valid; -1: unknown (a prefill / mixed step wrote d_bt)
-  ArgPair* h_pairs = nullptr;   // pinned
-  int32_t* h_tok = nullptr;     // pinned
-  int last_B = 0;
-  // on-device temperature sampling (K8s), armed per step by nvc_runner_set_sampling
-  float* d_temps = nullptr;
-  uint64_t* d_streams = nullptr;
-  float* h_temps = nullptr;        // pinned
-  uint64_t* h_streams = nullptr;   // pinned
-  bool sampling_armed = false;
-  int last_sampling_B = 0;
-  uint64_t sampling_seed = 0;
-  // decode graphs keyed by (B, 2 * blocks hint + sampling)
-  std::map<std::pair<int, int>, cudaGraphExec_t> graphs;
-  int launches_per_decode = 0;
-  int64_t last_h2d_bytes = 0;      // host-to-device bytes of the last step's inputs
-  bool x_nvls = false;             // r->x is the context's NVLS slot: all-reduces go through the switch
-  int last_decode_hint = 0;
-  int last_decode_key2 = 0;
-};
+using Layer = nvc_qwen3_layer;
+using ArgPair = nvc_arg_pair;
 
 namespace {
 
@@ -280,7 +219,23 @@ int finish_tokens(nvc_runner* r, int B, int32_t* out_tokens) {
   return collect_tokens(r, B, out_tokens);
 }
 
+// logits -> tokens for a registry model: the body has filled r->logits [rows, ld]; greedy argmax or the armed sampler
+int body_tokens(nvc_runner* r, int rows) {
+  const int V = r->body->vocab(), ld = r->body->logits_ld();
+  if (r->sampling_armed)
+    return nvc_sample_gumbel(r->ctx, r->logits, ld, r->d_temps, r->d_streams, r->sampling_seed, r->d_tok, r->d_tok_val, rows, V, 0,
+                             r->stream);
+  return nvc_argmax_last(r->ctx, r->logits, ld, r->d_tok, r->d_tok_val, rows, V, 0, r->stream);
+}
+
 int decode_body(nvc_runner* r, int B, int blocks_hint) {
+  if (r->body) {
+    nvc_step_shape sh;
+    sh.N = sh.B = sh.rows = B;
+    sh.decode = true;
+    int rc = r->body->forward(r, sh);
+    return rc ? rc : body_tokens(r, B);
+  }
   int rc = nvc_embed_gather(r->ctx, r->d_ids, r->embed, r->x, B, r->cfg.hidden_size, r->cfg.vocab_size, r->stream);
   if (rc) return rc;
   bool fnd = false;
@@ -297,6 +252,41 @@ int stage_sampling(nvc_runner* r, int B) {
   NVC_REQUIRE(r->ctx, r->last_sampling_B == B, NVC_ESTATE, "nvc_runner_set_sampling was armed for a different batch size");
   R_CUDA(cudaMemcpyAsync(r->d_temps, r->h_temps, B * sizeof(float), cudaMemcpyHostToDevice, r->stream));
   R_CUDA(cudaMemcpyAsync(r->d_streams, r->h_streams, B * sizeof(uint64_t), cudaMemcpyHostToDevice, r->stream));
+  return NVC_OK;
+}
+
+// step inputs, their pinned staging and the sampling state: what every model family needs
+int alloc_step_buffers(nvc_runner* r) {
+  const nvc_runner_options* opt = &r->opt;
+  const int tp = r->tp;
+  const size_t T = (size_t)std::max(opt->max_num_batched_tokens, opt->max_num_seqs);
+  const size_t Bm = (size_t)opt->max_num_seqs;
+  int rc;
+  {
+    r->in_pitch = (std::max(T, Bm) + 3) / 4 * 4;
+    int32_t* blk = nullptr;
+    if ((rc = dev_alloc(r, &blk, 4 * r->in_pitch))) return rc;
+    r->d_ids = blk;
+    r->d_pos = blk + r->in_pitch;
+    r->d_slots = blk + 2 * r->in_pitch;
+    r->d_ctx = blk + 3 * r->in_pitch;
+  }
+  if ((rc = dev_alloc(r, &r->d_cu, Bm + 1))) return rc;
+  if ((rc = dev_alloc(r, &r->d_cu2, Bm + 1))) return rc;
+  if ((rc = dev_alloc(r, &r->d_bt, Bm * r->max_blocks_cap))) return rc;
+  if ((rc = dev_alloc(r, &r->d_last_rows, std::max(Bm, (size_t)r->max_logit_rows)))) return rc;
+  if ((rc = dev_alloc(r, &r->d_tok, Bm))) return rc;
+  if ((rc = dev_alloc(r, &r->d_tok_val, Bm))) return rc;
+  if ((rc = dev_alloc(r, &r->d_pairs, Bm * tp))) return rc;
+  if ((rc = dev_alloc(r, &r->d_temps, Bm))) return rc;
+  if ((rc = dev_alloc(r, &r->d_streams, Bm))) return rc;
+  R_CUDA(cudaMallocHost(&r->h_temps, Bm * sizeof(float)));
+  R_CUDA(cudaMallocHost(&r->h_streams, Bm * sizeof(uint64_t)));
+  r->h_stage_ints = 3 * T + 2 * (Bm + 1) + Bm * r->max_blocks_cap + 2 * Bm + (size_t)r->max_logit_rows;
+  R_CUDA(cudaMallocHost(&r->h_stage, r->h_stage_ints * sizeof(int32_t)));
+  r->bt_mirror.assign(Bm * r->max_blocks_cap, -1);
+  R_CUDA(cudaMallocHost(&r->h_pairs, Bm * tp * sizeof(ArgPair)));
+  R_CUDA(cudaMallocHost(&r->h_tok, Bm * sizeof(int32_t)));
   return NVC_OK;
 }
 
@@ -384,36 +374,13 @@ int nvc_runner_create(nvc_ctx* ctx, const nvc_qwen3_config* cfg, const nvc_runne
   if ((rc = dev_alloc(r, &r->x_last, Bm * H))) return rc;
   if ((rc = dev_alloc(r, &r->xn_last, Bm * H))) return rc;
   if ((rc = dev_alloc(r, &r->res_last, Bm * H))) return rc;
-  if ((rc = dev_alloc(r, &r->logits, Bm * r->V_l))) return rc;
+  r->max_logit_rows = std::max((int)Bm, opt->max_logit_rows);
+  if ((rc = dev_alloc(r, &r->logits, (size_t)r->max_logit_rows * r->V_l))) return rc;
   r->decode_ws_bytes = 0;
   for (int b = 1; b <= opt->max_num_seqs; ++b)
     r->decode_ws_bytes = std::max(r->decode_ws_bytes, nvc_paged_decode_workspace_bytes(b, r->nh_l, hd, ctx->num_sms));
   if ((rc = dev_alloc(r, reinterpret_cast<uint8_t**>(&r->decode_ws), r->decode_ws_bytes))) return rc;
-  {
-    r->in_pitch = (std::max(T, Bm) + 3) / 4 * 4;
-    int32_t* blk = nullptr;
-    if ((rc = dev_alloc(r, &blk, 4 * r->in_pitch))) return rc;
-    r->d_ids = blk;
-    r->d_pos = blk + r->in_pitch;
-    r->d_slots = blk + 2 * r->in_pitch;
-    r->d_ctx = blk + 3 * r->in_pitch;
-  }
-  if ((rc = dev_alloc(r, &r->d_cu, Bm + 1))) return rc;
-  if ((rc = dev_alloc(r, &r->d_cu2, Bm + 1))) return rc;
-  if ((rc = dev_alloc(r, &r->d_bt, Bm * r->max_blocks_cap))) return rc;
-  if ((rc = dev_alloc(r, &r->d_last_rows, Bm))) return rc;
-  if ((rc = dev_alloc(r, &r->d_tok, Bm))) return rc;
-  if ((rc = dev_alloc(r, &r->d_tok_val, Bm))) return rc;
-  if ((rc = dev_alloc(r, &r->d_pairs, Bm * tp))) return rc;
-  if ((rc = dev_alloc(r, &r->d_temps, Bm))) return rc;
-  if ((rc = dev_alloc(r, &r->d_streams, Bm))) return rc;
-  R_CUDA(cudaMallocHost(&r->h_temps, Bm * sizeof(float)));
-  R_CUDA(cudaMallocHost(&r->h_streams, Bm * sizeof(uint64_t)));
-  r->h_stage_ints = 3 * T + 2 * (Bm + 1) + Bm * r->max_blocks_cap + 2 * Bm;
-  R_CUDA(cudaMallocHost(&r->h_stage, r->h_stage_ints * sizeof(int32_t)));
-  r->bt_mirror.assign(Bm * r->max_blocks_cap, -1);
-  R_CUDA(cudaMallocHost(&r->h_pairs, Bm * tp * sizeof(ArgPair)));
-  R_CUDA(cudaMallocHost(&r->h_tok, Bm * sizeof(int32_t)));
+  if ((rc = alloc_step_buffers(r))) return rc;
   return NVC_OK;
 }
 
@@ -429,6 +396,7 @@ int nvc_runner_destroy(nvc_runner* r) {
   if (r->h_temps) cudaFreeHost(r->h_temps);
   if (r->h_streams) cudaFreeHost(r->h_streams);
   if (r->stream) cudaStreamDestroy(r->stream);
+  delete r->body;
   delete r;
   return NVC_OK;
 }
@@ -441,6 +409,7 @@ int nvc_runner_get_options(const nvc_runner* r, nvc_runner_options* out) {
   return NVC_OK;
 }
 int64_t nvc_runner_kv_bytes_per_token(const nvc_runner* r) {
+  if (r && r->body) return r->body->cache_bytes_per_token();
   return r ? (int64_t)2 * r->cfg.num_hidden_layers * r->kv_l * r->cfg.head_dim * 2 : 0;
 }
 
@@ -476,6 +445,7 @@ extern "C" int nvc_runner_load_weight(nvc_runner* r, const char* hf_name, const 
   if (!r) return NVC_EINVAL;
   nvc_ctx* ctx = r->ctx;
   NVC_REQUIRE(ctx, hf_name && data, NVC_EINVAL, "null pointer");
+  NVC_REQUIRE(ctx, !r->body, NVC_ESTATE, "this runner takes its tensors through nvc_runner_load_tensor");
   NVC_CUDA_CHECK(ctx, cudaSetDevice(ctx->device));
   const nvc_qwen3_config& c = r->cfg;
   const int64_t H = c.hidden_size, hd = c.head_dim, V = c.vocab_size, I = c.intermediate_size;
@@ -552,6 +522,12 @@ extern "C" int nvc_runner_load_weight(nvc_runner* r, const char* hf_name, const 
 extern "C" int nvc_runner_finalize(nvc_runner* r) {
   if (!r) return NVC_EINVAL;
   nvc_ctx* ctx = r->ctx;
+  if (r->body) {
+    NVC_CUDA_CHECK(ctx, cudaSetDevice(ctx->device));
+    int rcb = r->body->finalize(r);
+    if (rcb == NVC_OK) r->finalized = true;
+    return rcb;
+  }
   const size_t want = 3 + 11 * (size_t)r->cfg.num_hidden_layers;
   NVC_REQUIRE(ctx, r->loaded.size() == want, NVC_ESTATE,
               "missing weights: " + std::to_string(r->loaded.size()) + " of " + std::to_string(want) +
@@ -585,8 +561,15 @@ int prefill_impl(nvc_runner* r, const int32_t* ids, const int32_t* positions, co
                 "bad cu_seqlens / max_seqlen");
   const int bs = r->opt.kvcache_block_size;
   const int64_t nslots = (int64_t)r->opt.num_kvcache_blocks * bs;
+  const int vocab = r->body ? r->body->vocab() : r->cfg.vocab_size;
+  NVC_REQUIRE(ctx, !r->body || paged, NVC_EINVAL, "this model attends through the paged cache: block_tables are required");
+  const bool use_armed = r->logit_rows_armed > 0;
+  const int rows = use_armed ? r->logit_rows_armed : B;
+  for (int i = 0; i < r->logit_rows_armed; ++i)
+    NVC_REQUIRE(ctx, r->armed_rows[i] >= 0 && r->armed_rows[i] < N, NVC_EINVAL, "armed logit row out of range");
+  r->logit_rows_armed = 0;   // one step only, also when the step fails below
   for (int i = 0; i < N; ++i) {
-    NVC_REQUIRE(ctx, ids[i] >= 0 && ids[i] < r->cfg.vocab_size, NVC_EINVAL, "token id out of range");
+    NVC_REQUIRE(ctx, ids[i] >= 0 && ids[i] < vocab, NVC_EINVAL, "token id out of range");
     NVC_REQUIRE(ctx, positions[i] >= 0 && positions[i] < r->opt.max_model_len, NVC_EINVAL, "position out of range");
     NVC_REQUIRE(ctx, slot_mapping[i] >= -1 && slot_mapping[i] < nslots, NVC_EINVAL, "slot out of range");
   }
@@ -618,12 +601,14 @@ int prefill_impl(nvc_runner* r, const int32_t* ids, const int32_t* positions, co
   memcpy(h + 3 * N, cu_seqlens, (B + 1) * 4);
   int32_t* last = h + 3 * N + B + 1;
   for (int b = 0; b < B; ++b) last[b] = cu_seqlens[b + 1] - 1;
+  int32_t* armed = h + r->h_stage_ints - r->max_logit_rows;   // the tail of the staging block
+  if (use_armed) memcpy(armed, r->armed_rows.data(), (size_t)rows * 4);
   cudaStream_t st = r->stream;
   R_CUDA(cudaMemcpyAsync(r->d_ids, h, N * 4, cudaMemcpyHostToDevice, st));
   R_CUDA(cudaMemcpyAsync(r->d_pos, h + N, N * 4, cudaMemcpyHostToDevice, st));
   R_CUDA(cudaMemcpyAsync(r->d_slots, h + 2 * N, N * 4, cudaMemcpyHostToDevice, st));
   R_CUDA(cudaMemcpyAsync(r->d_cu, h + 3 * N, (B + 1) * 4, cudaMemcpyHostToDevice, st));
-  R_CUDA(cudaMemcpyAsync(r->d_last_rows, last, B * 4, cudaMemcpyHostToDevice, st));
+  R_CUDA(cudaMemcpyAsync(r->d_last_rows, use_armed ? armed : last, (size_t)rows * 4, cudaMemcpyHostToDevice, st));
   r->last_h2d_bytes = (int64_t)N * 12 + (int64_t)(B + 1) * 4 + (int64_t)B * 4 +
                       (paged ? (int64_t)B * 4 + (int64_t)B * r->max_blocks_cap * 4 : 0);
   if (paged) {
@@ -653,6 +638,20 @@ int prefill_impl(nvc_runner* r, const int32_t* ids, const int32_t* positions, co
   }
   int rc = stage_sampling(r, B);
   if (rc) return rc;
+  if (r->body) {
+    nvc_step_shape sh;
+    sh.N = N; sh.B = B; sh.max_seqlen = max_seqlen; sh.rows = rows;
+    rc = r->body->forward(r, sh);
+    if (rc == NVC_OK && !use_armed) rc = body_tokens(r, B);
+    r->sampling_armed = false;
+    if (rc) return rc;
+    r->last_B = rows;
+    if (!use_armed) return finish_tokens(r, B, out_tokens);
+    R_CUDA(cudaStreamSynchronize(r->stream));
+    for (int b = 0; b < B; ++b) out_tokens[b] = -1;     // a step with armed logit rows samples nothing
+    return NVC_OK;
+  }
+  NVC_REQUIRE(ctx, !use_armed, NVC_ENOTIMPL, "armed logit rows need a registry model");
   rc = nvc_embed_gather(ctx, r->d_ids, r->embed, r->x, N, r->cfg.hidden_size, r->cfg.vocab_size, st);
   if (rc) return rc;
   bool fnd = false;
@@ -709,7 +708,7 @@ extern "C" int nvc_runner_decode(nvc_runner* r, const int32_t* ids, const int32_
   const int bs = r->opt.kvcache_block_size;
   const int64_t nslots = (int64_t)r->opt.num_kvcache_blocks * bs;
   for (int b = 0; b < B; ++b) {
-    NVC_REQUIRE(ctx, ids[b] >= 0 && ids[b] < r->cfg.vocab_size, NVC_EINVAL, "token id out of range");
+    NVC_REQUIRE(ctx, ids[b] >= 0 && ids[b] < (r->body ? r->body->vocab() : r->cfg.vocab_size), NVC_EINVAL, "token id out of range");
     NVC_REQUIRE(ctx, positions[b] >= 0 && positions[b] < r->opt.max_model_len, NVC_EINVAL, "position out of range");
     NVC_REQUIRE(ctx, slot_mapping[b] >= 0 && slot_mapping[b] < nslots, NVC_EINVAL, "slot out of range");
     NVC_REQUIRE(ctx, context_lens[b] > 0 && (int64_t)context_lens[b] <= (int64_t)max_blocks * bs, NVC_EINVAL, "context_len vs block table");
@@ -828,7 +827,9 @@ extern "C" int nvc_runner_last_logits(nvc_runner* r, float* out, int B) {
   nvc_ctx* ctx = r->ctx;
   NVC_REQUIRE(ctx, out && B > 0 && B <= r->last_B, NVC_EINVAL, "no logits for that batch");
   NVC_CUDA_CHECK(ctx, cudaSetDevice(ctx->device));
-  R_CUDA(cudaMemcpyAsync(out, r->logits, (size_t)B * r->V_l * sizeof(float), cudaMemcpyDeviceToHost, r->stream));
+  const size_t V = r->body ? (size_t)r->body->vocab() : (size_t)r->V_l, ld = r->body ? (size_t)r->body->logits_ld() : V;
+  R_CUDA(cudaMemcpy2DAsync(out, V * sizeof(float), r->logits, ld * sizeof(float), V * sizeof(float), (size_t)B, cudaMemcpyDeviceToHost,
+                           r->stream));
   R_CUDA(cudaStreamSynchronize(r->stream));
   return NVC_OK;
 }
@@ -877,6 +878,7 @@ extern "C" int nvc_runner_time_op(nvc_runner* r, int op, int iters, float* ms_pe
   if (!r) return NVC_EINVAL;
   nvc_ctx* ctx = r->ctx;
   NVC_REQUIRE(ctx, ms_per_launch && iters > 0, NVC_EINVAL, "bad arguments");
+  NVC_REQUIRE(ctx, !r->body, NVC_ENOTIMPL, "per-kernel timing covers the built-in Qwen3 body");
   NVC_REQUIRE(ctx, r->last_B > 0 && r->last_decode_hint > 0, NVC_ESTATE, "no decode step has run yet");
   NVC_CUDA_CHECK(ctx, cudaSetDevice(ctx->device));
   const nvc_qwen3_config& c = r->cfg;
@@ -976,3 +978,76 @@ extern "C" int nvc_runner_time_op(nvc_runner* r, int op, int iters, float* ms_pe
   if (launches) *launches = kernels;
   return NVC_OK;
 }
+
+// ------------------------------------------------------------------------------------------
+// registry models
+// ------------------------------------------------------------------------------------------
+nvc_model_body* nvc_make_karuzen_body(nvc_runner* r, const nvc_karuzen_config& cfg, int* status);   // model_karuzen.cu
+
+extern "C" int nvc_runner_create_from_config(nvc_ctx* ctx, const nvc_model_config* mc, const nvc_runner_options* opt,
+                                             nvc_runner** out) {
+  NVC_REQUIRE(ctx, ctx && mc && opt && out, NVC_EINVAL, "null pointer");
+  *out = nullptr;
+  if (mc->architecture == "Qwen3ForCausalLM") {
+    NVC_REQUIRE(ctx, opt->dtype == NVC_DT_BF16, NVC_ENOTIMPL, "the Qwen3 body runs in bf16 only");
+    return nvc_runner_create(ctx, &mc->qwen3, opt, out);
+  }
+  NVC_REQUIRE(ctx, mc->architecture == "Karuzen", NVC_ENOTIMPL, "architecture " + mc->architecture + " has no model body");
+  NVC_REQUIRE(ctx, ctx->tp_size == 1, NVC_ENOTIMPL, "Karuzen runs on one GPU");
+  NVC_REQUIRE(ctx, opt->dtype == NVC_DT_BF16 || opt->dtype == NVC_DT_F32, NVC_EINVAL, "dtype must be NVC_DT_BF16 or NVC_DT_F32");
+  NVC_REQUIRE(ctx, opt->num_kvcache_blocks > 0 && opt->kvcache_block_size > 0 && opt->max_num_seqs > 0 &&
+                       opt->max_num_batched_tokens > 0 && opt->max_model_len > 0, NVC_EINVAL, "bad runner options");
+  NVC_CUDA_CHECK(ctx, cudaSetDevice(ctx->device));
+  nvc_runner* r = new nvc_runner();
+  r->ctx = ctx;
+  r->opt = *opt;
+  r->dtype = opt->dtype;
+  r->tp = 1;
+  r->rank = 0;
+  r->max_blocks_cap = (opt->max_model_len + opt->kvcache_block_size - 1) / opt->kvcache_block_size;
+  r->max_logit_rows = std::max(opt->max_num_seqs, opt->max_logit_rows);
+  *out = r;
+  R_CUDA(cudaStreamCreateWithFlags(&r->stream, cudaStreamNonBlocking));
+  int rc = NVC_OK;
+  r->body = nvc_make_karuzen_body(r, mc->karuzen, &rc);
+  if (rc) return rc;
+  r->V_l = r->body->vocab();
+  if ((rc = dev_alloc(r, &r->logits, (size_t)r->max_logit_rows * r->body->logits_ld()))) return rc;
+  return alloc_step_buffers(r);
+}
+
+extern "C" int nvc_runner_load_tensor(nvc_runner* r, const char* name, const void* data, int st_dtype, const int64_t* shape,
+                                      int ndim) {
+  if (!r) return NVC_EINVAL;
+  nvc_ctx* ctx = r->ctx;
+  NVC_REQUIRE(ctx, name && data && (shape || ndim == 0) && ndim >= 0 && ndim <= 4, NVC_EINVAL, "bad arguments");
+  NVC_REQUIRE(ctx, r->body, NVC_ESTATE, "the built-in Qwen3 body takes its tensors through nvc_runner_load_weight");
+  NVC_CUDA_CHECK(ctx, cudaSetDevice(ctx->device));
+  return r->body->load_tensor(r, name, data, st_dtype, shape, ndim);
+}
+
+extern "C" int nvc_runner_takes_raw_tensors(const nvc_runner* r) { return r && r->body ? 1 : 0; }
+extern "C" int nvc_runner_needs_block_tables(const nvc_runner* r) { return r && r->body ? 1 : 0; }
+extern "C" int nvc_runner_vocab(const nvc_runner* r) { return !r ? 0 : (r->body ? r->body->vocab() : r->cfg.vocab_size); }
+
+extern "C" int nvc_runner_set_logit_rows(nvc_runner* r, const int32_t* rows, int n) {
+  if (!r) return NVC_EINVAL;
+  nvc_ctx* ctx = r->ctx;
+  if (!rows || n == 0) {
+    r->logit_rows_armed = 0;
+    return NVC_OK;
+  }
+  NVC_REQUIRE(ctx, r->body, NVC_ENOTIMPL, "armed logit rows need a registry model");
+  NVC_REQUIRE(ctx, n > 0 && n <= r->max_logit_rows, NVC_ENOMEM, "more logit rows than the runner was created for (max_logit_rows)");
+  r->armed_rows.assign(rows, rows + n);
+  r->logit_rows_armed = n;
+  return NVC_OK;
+}
+
+extern "C" int nvc_runner_set_residual_tap(nvc_runner* r, float* host, int64_t capacity_floats) {
+  if (!r) return NVC_EINVAL;
+  NVC_REQUIRE(r->ctx, r->body, NVC_ENOTIMPL, "the residual tap needs a registry model");
+  return r->body->set_residual_tap(host, (size_t)std::max<int64_t>(capacity_floats, 0));
+}
+extern "C" int nvc_runner_layer_runs(const nvc_runner* r) { return r && r->body ? r->body->layer_runs() : 0; }
+extern "C" int nvc_runner_width(const nvc_runner* r) { return !r ? 0 : (r->body ? r->body->width() : r->cfg.hidden_size); }

@@ -149,6 +149,22 @@ MODEL_CONFIGS: Dict[str, Qwen3Config] = {
 }
 
 
+class DeviceContext:
+    """nvc_ctx for callers that need no tensor library (the command-line tools): one per (process, device)."""
+
+    def __init__(self, device: int = 0):
+        self.l = _lib.lib()
+        h = C.c_void_p()
+        check(self.l.nvc_ctx_create(device, 0, 1, C.byref(h)), "nvc_ctx_create")
+        self.h = h
+        self.device, self.tp_rank, self.tp_size = device, 0, 1
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.l.nvc_ctx_destroy(self.h)
+            self.h = None
+
+
 # ----------------------------------------------------------------------------- runners
 class DummyModelRunner:
     """next token = last_token + 1 (implemented inside the C++ engine when no runner is given)."""
@@ -319,6 +335,124 @@ class Qwen3ModelRunner:
         return self.l.nvc_runner_kv_bytes_per_token(self.handle)
 
 
+class ModelRunner(Qwen3ModelRunner):
+    """A runner for any registered architecture, chosen by config.json (the model registry lives in the library:
+    "Qwen3ForCausalLM" -> the Qwen3 body, "Karuzen" -> the Karuzen body).  Same step methods as
+    Qwen3ModelRunner; registry models attend through the paged cache, so their steps are `decode`
+    and `step_mixed` (the engine drives them the same way).
+
+    dtype: "bfloat16" (serving: bf16 storage and tensor-core products, fp32 residual / norms /
+    softmax / routers) or "float32" (exact mode: everything in IEEE fp32 on the FMA pipe)."""
+
+    DTYPES = {"bfloat16": 0, "float32": 1}
+
+    def __init__(self, ctx, config_handle, num_kvcache_blocks: int, kvcache_block_size: int = 64, max_num_seqs: int = 64,
+                 max_num_batched_tokens: int = 4096, max_model_len: Optional[int] = None, use_cuda_graph: bool = True,
+                 dtype: str = "bfloat16", max_logit_rows: int = 0):
+        self.l = _lib.lib()
+        self.ctx = ctx
+        self.architecture = self.l.nvc_model_config_architecture(config_handle).decode()
+        self.dtype = dtype
+        self.block_size = kvcache_block_size
+        self.num_kvcache_blocks = num_kvcache_blocks
+        max_model_len = max_model_len or num_kvcache_blocks * kvcache_block_size
+        self.max_model_len = max_model_len
+        self.max_num_seqs, self.max_num_batched_tokens = max_num_seqs, max_num_batched_tokens
+        opt = RunnerOptionsC(num_kvcache_blocks, kvcache_block_size, max_num_seqs, max_num_batched_tokens, max_model_len,
+                             1 if use_cuda_graph else 0, 0, self.DTYPES[dtype], max_logit_rows)
+        h = C.c_void_p()
+        st = self.l.nvc_runner_create_from_config(ctx.h, config_handle, C.byref(opt), C.byref(h))
+        self.handle = h
+        if st != 0:
+            msg = self.l.nvc_last_error(ctx.h).decode()
+            self.close()
+            raise NvcError(st, "nvc_runner_create_from_config", msg)
+        self.vocab_size = self.l.nvc_runner_vocab(self.handle)
+        if self.architecture == "Qwen3ForCausalLM":
+            qc, tie = Qwen3ConfigC(), C.c_int()
+            self.l.nvc_model_config_qwen3(config_handle, C.byref(qc), C.byref(tie))
+            self.cfg = Qwen3Config(**{n: getattr(qc, n) for n in Qwen3Config.__dataclass_fields__
+                                      if n not in ("hidden_act", "tie_word_embeddings")})
+            self.eos_id = self.cfg.eos_token_id
+        else:
+            self.cfg = None
+            self.eos_id = -1          # the design has no end-of-sequence token
+        self._final = False
+
+    @staticmethod
+    def _config(model_dir: Optional[str] = None, config: Optional[dict] = None):
+        l = _lib.lib()
+        h = C.c_void_p()
+        if model_dir is not None:
+            st = l.nvc_model_config_load(os.fsencode(model_dir), C.byref(h))
+        else:
+            st = l.nvc_model_config_from_json(json.dumps(config).encode(), C.byref(h))
+        if st != 0:
+            raise NvcError(st, "nvc_model_config_load", l.nvc_model_config_last_error().decode())
+        return h
+
+    @classmethod
+    def from_dir(cls, ctx, model_dir: str, **kw) -> "ModelRunner":
+        """config.json + model.safetensors of any registered architecture, read by the native loader."""
+        ch = cls._config(model_dir=model_dir)
+        try:
+            r = cls(ctx, ch, **kw)
+        finally:
+            _lib.lib().nvc_model_config_free(ch)
+        st = r.l.nvc_runner_load_hf_dir(r.handle, os.fsencode(model_dir))
+        if st != 0:
+            msg = r.l.nvc_hf_last_error().decode() + " | " + r.l.nvc_last_error(ctx.h).decode()
+            r.close()
+            raise NvcError(st, "nvc_runner_load_hf_dir", msg)
+        r._final = True
+        return r
+
+    @classmethod
+    def from_config(cls, ctx, config: dict, weights: Iterable[Tuple[str, "torch.Tensor"]], **kw) -> "ModelRunner":
+        """config: the dict a config.json would hold; weights: (name, CPU tensor) pairs under the checkpoint's names."""
+        ch = cls._config(config=config)
+        try:
+            r = cls(ctx, ch, **kw)
+        finally:
+            _lib.lib().nvc_model_config_free(ch)
+        for name, t in weights:
+            r.load_tensor(name, t)
+        r.finalize()
+        return r
+
+    def load_tensor(self, name: str, t) -> None:
+        import torch
+        if not self.l.nvc_runner_takes_raw_tensors(self.handle):
+            return self.load_weight(name, t)
+        t = t.detach().cpu().contiguous()
+        kinds = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+        if t.dtype not in kinds:
+            t = t.float()
+        shape = (C.c_int64 * max(t.dim(), 1))(*t.shape)
+        st = self.l.nvc_runner_load_tensor(self.handle, name.encode(), C.c_void_p(t.data_ptr()), kinds[t.dtype], shape, t.dim())
+        check(st, f"nvc_runner_load_tensor({name})", self.ctx.h)
+
+    def set_logit_rows(self, rows) -> None:
+        """The next prefill / mixed step computes logits for these flat token rows (None disarms)."""
+        if rows is None or len(rows) == 0:
+            check(self.l.nvc_runner_set_logit_rows(self.handle, None, 0), "nvc_runner_set_logit_rows", self.ctx.h)
+            return
+        a = _i32(rows)
+        check(self.l.nvc_runner_set_logit_rows(self.handle, _p(a), len(a)), "nvc_runner_set_logit_rows", self.ctx.h)
+
+    def last_logits(self, B: int) -> np.ndarray:
+        out = np.empty((B, self.vocab_size // self.ctx.tp_size), dtype=np.float32)
+        check(self.l.nvc_runner_last_logits(self.handle, _p(out), B), "nvc_runner_last_logits", self.ctx.h)
+        return out
+
+    def tap_residual(self, num_tokens: int) -> np.ndarray:
+        """Arms the debug tap for the next step; the returned array [layer runs, tokens, width] is filled by that step."""
+        runs, width = self.l.nvc_runner_layer_runs(self.handle), self.l.nvc_runner_width(self.handle)
+        buf = np.zeros((runs, num_tokens, width), dtype=np.float32)
+        check(self.l.nvc_runner_set_residual_tap(self.handle, _p(buf), buf.size), "nvc_runner_set_residual_tap", self.ctx.h)
+        return buf
+
+
 # ----------------------------------------------------------------------------- engine
 @dataclass
 class GenerationOutput:
@@ -461,6 +595,31 @@ class LLMEngine:
             for sid, toks in s.outputs:
                 outs[sid] = toks
         return [GenerationOutput(sid, outs[sid]) for sid in sorted(outs)]
+
+    # -- caller-driven requests: the caller says which tokens each step computes ------------------
+    def open_request(self) -> int:
+        sid = self.l.nvc_engine_open_request(self.h)
+        if sid < 0:
+            self._ck(int(sid), "nvc_engine_open_request")
+        return int(sid)
+
+    def close_request(self, seq_id: int) -> None:
+        self._ck(self.l.nvc_engine_close_request(self.h, seq_id), "nvc_engine_close_request")
+
+    def step_forced(self, entries: Seq[Tuple[int, Seq[int], Seq[int]]]) -> Optional[np.ndarray]:
+        """One step over exactly `entries` = (seq_id, next tokens, offsets among them whose logits are wanted).
+        The tokens are appended to their requests and computed on top of the cache; returns the
+        fp32 logits [wanted, vocab] in entry order (None when nothing is wanted).  Nothing is sampled."""
+        ids = np.ascontiguousarray(np.asarray([e[0] for e in entries], dtype=np.int64))
+        counts = _i32([len(e[1]) for e in entries])
+        toks = _i32([t for e in entries for t in e[1]])
+        wc = _i32([len(e[2]) for e in entries])
+        wo = _i32([o for e in entries for o in e[2]])
+        so = StepOutputC()
+        self._ck(self.l.nvc_engine_step_forced(self.h, len(entries), _p(ids), _p(counts), _p(toks), _p(wc), _p(wo), C.byref(so)),
+                 "nvc_engine_step_forced")
+        n = int(wc.sum())
+        return self.model_runner.last_logits(n) if n else None
 
     # -- pieces of step(), exposed for the contract tests and the benchmark ----------------------
     def schedule(self) -> StepInputs:

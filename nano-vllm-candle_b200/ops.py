@@ -295,3 +295,119 @@ class Context:
                                           C.c_uint64(seed & (2 ** 64 - 1)), _ptr(idx), _ptr(val), B, V, index_offset,
                                           _stream()), "nvc_sample_gumbel")
         return idx, val
+
+
+# ----------------------------------------------------------------------------- fp32-residual mechanisms
+# (Dynamic-Tanh norm, latent attention, mixture-of-experts routing, the FMA matrix products of the exact mode).
+# Tensors are torch.bfloat16 (serving) or torch.float32 (exact mode); the dtype of the data picks the kernel.
+ACT_NONE, ACT_RELU2, ACT_GELU_TANH_MUL = 0, 1, 2
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return 0
+    if t.dtype == torch.float32:
+        return 1
+    raise TypeError(f"bf16 or fp32 expected, got {t.dtype}")
+
+
+def embed_gather_f32(ctx, ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    N, H = ids.numel(), table.shape[1]
+    out = torch.empty(N, H, dtype=torch.float32, device=table.device)
+    check(ctx.l.nvc_embed_gather_f32(ctx.h, _ptr(ids), _ptr(table), _dt(table), table.stride(0), _ptr(out), H, N, H, _stream()),
+          "nvc_embed_gather_f32", ctx.h)
+    return out
+
+
+def dyt_norm(ctx, res: torch.Tensor, addends, w, b, alpha, out_dtype=torch.bfloat16, rows=None, write_back=True):
+    """(updated residual or None, normed rows or None): residual += sum(addends); DyT of the rows when w is given."""
+    N = res.shape[0] if rows is None else rows.numel()
+    H = res.shape[1]
+    a = list(addends) + [None] * (3 - len(addends))
+    out = torch.empty(N, H, dtype=out_dtype, device=res.device) if w is not None else None
+    ro = res if (write_back and rows is None) else None
+    check(ctx.l.nvc_dyt_norm(ctx.h, _ptr(res), _ptr(a[0]), _ptr(a[1]), _ptr(a[2]), _ptr(ro), res.stride(0), _ptr(w), _ptr(b),
+                             _ptr(alpha), _ptr(out), _dt(out) if out is not None else 0, H, _ptr(rows), N, H, _stream()),
+          "nvc_dyt_norm", ctx.h)
+    return ro, out
+
+
+def latent_norm_store(ctx, x: torch.Tensor, n0: int, off1: int, n1: int, w0, w1, eps: float, cache, slot_mapping, dtype):
+    """x: fp32 [N, ld]; returns the normed query latent [N, n0]; the key/value latent goes to cache[slot]."""
+    N = x.shape[0]
+    out0 = torch.empty(N, n0, dtype=dtype, device=x.device)
+    check(ctx.l.nvc_latent_norm_store(ctx.h, _ptr(x), x.stride(0), n0, off1, n1, _ptr(w0), _ptr(w1), eps, _ptr(out0), n0,
+                                      _ptr(cache), cache.stride(0) if cache is not None else 0, _ptr(slot_mapping), _dt(out0), N,
+                                      _stream()), "nvc_latent_norm_store", ctx.h)
+    return out0
+
+
+def act_mul(ctx, x: torch.Tensor, F: int, kind: int) -> torch.Tensor:
+    N = x.shape[0]
+    out = torch.empty(N, F, dtype=x.dtype, device=x.device)
+    check(ctx.l.nvc_act_mul(ctx.h, _ptr(x), x.stride(0), _ptr(out), F, _dt(x), N, F, F, kind, _stream()), "nvc_act_mul", ctx.h)
+    return out
+
+
+def linear(ctx, A: torch.Tensor, W: torch.Tensor, out_dtype=None, act: int = ACT_NONE) -> torch.Tensor:
+    """A [M, K] or [batch, M, K]; W [N, K] or [batch, N, K]: act(A . W^T) on the FMA pipe."""
+    batched = A.dim() == 3
+    Bn = A.shape[0] if batched else 1
+    M, K, N = A.shape[-2], A.shape[-1], W.shape[-2]
+    out_dtype = out_dtype or A.dtype
+    C_ = torch.empty((Bn, M, N) if batched else (M, N), dtype=out_dtype, device=A.device)
+    check(ctx.l.nvc_linear(ctx.h, _ptr(A), A.stride(-2), A.stride(0) if batched else 0, _ptr(W), W.stride(-2),
+                           W.stride(0) if batched else 0, _ptr(C_), N, M * N if batched else 0, _dt(A), _dt(C_), M, N, K, Bn, act,
+                           _stream()), "nvc_linear", ctx.h)
+    return C_
+
+
+def linear_grouped(ctx, A, a_rows, W, offsets, rows: int, out_dtype=None, act: int = ACT_NONE) -> torch.Tensor:
+    """W [groups, N, K]; rows [offsets[g], offsets[g + 1]) of the result use W[g] on A[a_rows[r]]."""
+    G, N, K = W.shape
+    out_dtype = out_dtype or A.dtype
+    C_ = torch.zeros(rows, N, dtype=out_dtype, device=A.device)
+    check(ctx.l.nvc_linear_grouped(ctx.h, _ptr(A), A.stride(0), _ptr(a_rows), _ptr(W), K, N * K, _ptr(C_), N, _ptr(offsets), G, rows,
+                                   _dt(A), _dt(C_), N, K, act, _stream()), "nvc_linear_grouped", ctx.h)
+    return C_
+
+
+def moe_route(ctx, h, w_router, correction, w_gate, top: int, scale: float):
+    N, H = h.shape
+    E = w_router.shape[0]
+    idx = torch.empty(N, top, dtype=torch.int32, device=h.device)
+    w = torch.empty(N, top, dtype=torch.float32, device=h.device)
+    gate = torch.empty(N, dtype=torch.float32, device=h.device) if w_gate is not None else None
+    check(ctx.l.nvc_moe_route(ctx.h, _ptr(h), _dt(h), h.stride(0), _ptr(w_router), _ptr(correction), _ptr(w_gate), E, top, scale,
+                              _ptr(idx), _ptr(w), _ptr(gate), N, H, _stream()), "nvc_moe_route", ctx.h)
+    return idx, w, gate
+
+
+def moe_sort(ctx, idx: torch.Tensor, E: int):
+    N, top = idx.shape
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=idx.device)
+    src = torch.empty(N * top, dtype=torch.int32, device=idx.device)
+    pos = torch.empty(N * top, dtype=torch.int32, device=idx.device)
+    check(ctx.l.nvc_moe_sort(ctx.h, _ptr(idx), N, top, E, _ptr(offsets), _ptr(src), _ptr(pos), _stream()), "nvc_moe_sort", ctx.h)
+    return offsets, src, pos
+
+
+def moe_combine(ctx, y, pos, w, shared=None, gate=None) -> torch.Tensor:
+    N, top = w.shape
+    H = y.shape[1]
+    out = torch.empty(N, H, dtype=torch.float32, device=y.device)
+    check(ctx.l.nvc_moe_combine(ctx.h, _ptr(y), _dt(y), y.stride(0), _ptr(pos), _ptr(w), top, _ptr(shared),
+                                _dt(shared) if shared is not None else 0, shared.stride(0) if shared is not None else 0, _ptr(gate),
+                                _ptr(out), H, N, H, _stream()), "nvc_moe_combine", ctx.h)
+    return out
+
+
+def latent_attn_paged(ctx, q, cache, block_tables, context_lens, cu_seqlens, max_qlen: int, block_size: int, scale: float):
+    """q: [rows, heads, D]; cache: [slots, >= D]; returns the attended latents [rows, heads, D]."""
+    rows, heads, D = q.shape
+    out = torch.empty_like(q)
+    B = context_lens.numel()
+    check(ctx.l.nvc_latent_attn_paged(ctx.h, _ptr(q), heads * D, _ptr(cache), cache.stride(0), _ptr(block_tables),
+                                      block_tables.stride(0), _ptr(context_lens), _ptr(cu_seqlens), B, max_qlen, heads, D, D,
+                                      block_size, scale, _ptr(out), heads * D, _dt(q), _stream()), "nvc_latent_attn_paged", ctx.h)
+    return out

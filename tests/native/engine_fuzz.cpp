@@ -147,6 +147,10 @@ int nvc_runner_get_options(const nvc_runner* r, nvc_runner_options* o) {
 }
 int nvc_runner_load_weight(nvc_runner*, const char*, const nvc_bf16*, int64_t, int64_t) { return 0; }
 int nvc_runner_finalize(nvc_runner*) { return 0; }
+int nvc_runner_load_tensor(nvc_runner*, const char*, const void*, int, const int64_t*, int) { return 0; }
+int nvc_runner_takes_raw_tensors(const nvc_runner*) { return 0; }
+int nvc_runner_needs_block_tables(const nvc_runner*) { return 0; }
+int nvc_runner_set_logit_rows(nvc_runner*, const int32_t*, int) { return 0; }
 }
 
 // Phase 2: the HF loader's JSON / safetensors readers on mutated files (argv[3] = scratch directory).
