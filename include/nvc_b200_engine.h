@@ -80,6 +80,9 @@ int nvc_model_config_from_json(const char* json_text, nvc_model_config** out);
 void nvc_model_config_free(nvc_model_config* c);
 const char* nvc_model_config_architecture(const nvc_model_config* c);
 int nvc_model_config_vocab(const nvc_model_config* c);
+/* Karuzen: the order in which layers run (a looped block repeats), which pass each run belongs to (each has its own cache)
+ * and whether the embedding is added again before it; returns the number of runs (fills at most `capacity`). */
+int nvc_model_config_layer_runs(const nvc_model_config* c, int32_t* layers, int32_t* passes, int32_t* readd, int capacity);
 int nvc_model_config_qwen3(const nvc_model_config* c, nvc_qwen3_config* out, int* tie_word_embeddings);
 /* A runner for the configured architecture (Qwen3: same as nvc_runner_create).  opt->dtype selects the storage format
  * of a registry model; its steps attend through the paged cache, so they take block_tables (nvc_runner_prefill_paged,

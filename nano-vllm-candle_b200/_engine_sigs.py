@@ -62,6 +62,7 @@ def declare(l: C.CDLL) -> None:
         "nvc_model_config_load": [C.c_char_p, C.POINTER(_vp)],
         "nvc_model_config_from_json": [C.c_char_p, C.POINTER(_vp)],
         "nvc_model_config_vocab": [_vp],
+        "nvc_model_config_layer_runs": [_vp, _vp, _vp, _vp, _i],
         "nvc_model_config_qwen3": [_vp, C.POINTER(Qwen3ConfigC), C.POINTER(C.c_int)],
         "nvc_runner_create_from_config": [_vp, _vp, C.POINTER(RunnerOptionsC), C.POINTER(_vp)],
         "nvc_runner_load_tensor": [_vp, C.c_char_p, _vp, _i, C.POINTER(C.c_int64), _i],

@@ -160,6 +160,16 @@ int nvc_model_config_vocab(const nvc_model_config* c) {
   if (!c) return 0;
   return c->architecture == "Karuzen" ? c->karuzen.vocab : c->qwen3.vocab_size;
 }
+int nvc_model_config_layer_runs(const nvc_model_config* c, int32_t* layers, int32_t* passes, int32_t* readd, int capacity) {
+  if (!c || c->architecture != "Karuzen") return NVC_EINVAL;
+  const auto runs = c->karuzen.runs();
+  for (int i = 0; i < (int)runs.size() && i < capacity; ++i) {
+    if (layers) layers[i] = runs[i].layer;
+    if (passes) passes[i] = runs[i].pass;
+    if (readd) readd[i] = runs[i].readd_embedding ? 1 : 0;
+  }
+  return (int)runs.size();
+}
 int nvc_model_config_qwen3(const nvc_model_config* c, nvc_qwen3_config* out, int* tied) {
   if (!c || !out || c->architecture != "Qwen3ForCausalLM") return NVC_EINVAL;
   *out = c->qwen3;
