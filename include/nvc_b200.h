@@ -330,7 +330,8 @@ int nvc_moe_combine(nvc_ctx* ctx, const void* y, int y_dtype, int ldy, const int
  *   out[i, h, :D] = sum_{j <= pos_i} softmax_j(scale * q[i, h, :D] . c_j) * c_j,   c_j = cache[slot of token j, :D].
  * q / out: [rows, heads, head_stride] with row strides ldq / ldo; sequence b owns rows cu_seqlens[b] .. cu_seqlens[b + 1]
  * (cu_seqlens == NULL: one row per sequence), which are the LAST positions of its context_lens[b] tokens; the slot of token
- * j is block_tables[b, j / block_size] * block_size + j % block_size.  D <= 512. */
+ * j is block_tables[b, j / block_size] * block_size + j % block_size.  D <= 512.  bf16 rows with head_stride 64 or 128 run
+ * on the tensor pipe and read head_stride numbers per row: columns [D, head_stride) of q and of the cache rows must be zero. */
 int nvc_latent_attn_paged(nvc_ctx* ctx, const void* q, int ldq, const void* cache, int ldc, const int32_t* block_tables,
                           int bt_stride, const int32_t* context_lens, const int32_t* cu_seqlens, int B, int max_qlen, int heads,
                           int D, int head_stride, int block_size, float scale, void* out, int ldo, int dtype, void* stream);

@@ -6,8 +6,12 @@
 // A sequence contributes q_len >= 1 query tokens that are the LAST positions of its context (q_len = 1: decode; more: a
 // prompt or a portion of one behind an already cached prefix); all sequences of a step run in one launch.
 //
-// nvc_latent_attn_paged: fp32 FMA kernel for both storage formats (the exact mode and any D).
+// nvc_latent_attn_paged: the tensor-pipe kernel (latent_attn_mma.cuh) for bf16 rows of 64 or 128 numbers, else the fp32 FMA
+// kernel below (the exact mode, and any other width).
+#include <cstdlib>
+
 #include "typed.cuh"
+#include "latent_attn_mma.cuh"
 
 namespace {
 
@@ -118,6 +122,26 @@ extern "C" int nvc_latent_attn_paged(nvc_ctx* ctx, const void* q, int ldq, const
   NVC_REQUIRE(ctx, D <= 32 * kMaxDPerLane, NVC_ESHAPE, "latent size above 512");
   NVC_REQUIRE(ctx, head_stride >= D && ldq >= heads * head_stride && ldo >= heads * head_stride && ldc >= D, NVC_EINVAL, "bad strides");
   if (B == 0) return NVC_OK;
+  static const bool mma_env = !(getenv("NVC_LATENT_ATTN_MMA") && atoi(getenv("NVC_LATENT_ATTN_MMA")) == 0);
+  if (dtype == NVC_DT_BF16 && mma_env && (head_stride == 64 || head_stride == 128) && ldc >= head_stride && ldc % 8 == 0 &&
+      ldq % 2 == 0 && ldo % 2 == 0 && ((uintptr_t)cache % 16) == 0 && ((uintptr_t)q % 4) == 0) {
+    // padding columns [D, head_stride) of q and of the cache rows are zero by contract
+    const dim3 grid(((size_t)max_qlen * heads + 15) / 16, B);
+    const float sl2 = scale * 1.4426950408889634f;
+    if (head_stride == 64) {
+      NVC_CUDA_CHECK(ctx, nvc_launch(ctx, latmma::latent_attn_mma_kernel<64>, grid, dim3(latmma::kWarps * 32), latmma::smem_bytes<64>(),
+                                     nvc_stream(stream), reinterpret_cast<const nvc_bf16*>(q), ldq, reinterpret_cast<const nvc_bf16*>(cache),
+                                     ldc, block_tables, bt_stride, context_lens, cu_seqlens, heads, head_stride, block_size, sl2,
+                                     reinterpret_cast<nvc_bf16*>(out), ldo));
+    } else {
+      NVC_CUDA_CHECK(ctx, nvc_launch(ctx, latmma::latent_attn_mma_kernel<128>, grid, dim3(latmma::kWarps * 32), latmma::smem_bytes<128>(),
+                                     nvc_stream(stream), reinterpret_cast<const nvc_bf16*>(q), ldq, reinterpret_cast<const nvc_bf16*>(cache),
+                                     ldc, block_tables, bt_stride, context_lens, cu_seqlens, heads, head_stride, block_size, sl2,
+                                     reinterpret_cast<nvc_bf16*>(out), ldo));
+    }
+    ctx->launches++;
+    return NVC_OK;
+  }
   const size_t smem = ((size_t)kKeys * (D + 1) + (size_t)kRows * D) * sizeof(float);
   const dim3 grid(((size_t)max_qlen * heads + kRows - 1) / kRows, B);
   NVC_DISPATCH_DT(dtype, T, {

@@ -218,23 +218,27 @@ def test_latent_attention_decode_rows_without_cu_seqlens(ctx, ops, dt):
     assert torch.allclose(out.float().cpu(), want, **tol(dt))
 
 
-@pytest.mark.parametrize("where", [0, 1, 63, 64, 255, 256, 700])
-def test_latent_attention_finds_one_far_key(ctx, ops, where):
-    """One key among hundreds carries the whole weight: a lost page or an off-by-one in the causal bound shows."""
+@pytest.mark.parametrize("dt,D", [(torch.float32, 32), (torch.bfloat16, 64), (torch.bfloat16, 128), (torch.bfloat16, 24)])
+@pytest.mark.parametrize("where", [0, 1, 15, 16, 63, 64, 255, 256, 699, 700])
+def test_latent_attention_finds_one_far_key(ctx, ops, where, dt, D):
+    """One key among hundreds carries the whole weight: a lost page or tile, or an off-by-one in the causal bound, shows."""
     g = torch.Generator().manual_seed(15)
-    heads, D, bs, Tk = 2, 32, 64, 701
+    heads, bs, Tk = 2, 64, 701
     c = torch.randn(Tk, D, generator=g) * 0.1
     q = torch.randn(1, heads, D, generator=g) * 0.1
     c[where] = 4.0 * q[0, 0] / q[0, 0].norm()
     q[0, 0] = 40.0 * q[0, 0] / q[0, 0].norm()
-    cache, bt, cl = paged([c], bs, 16, torch.float32, 16)
-    out = ops.latent_attn_paged(ctx, q.to(DEV), cache, bt, cl, None, 1, bs, 1.0)
-    assert torch.allclose(out[0, 0].cpu(), c[where], atol=1e-3)
-    assert torch.allclose(out.cpu(), attn_want(q, c, 1.0), rtol=1e-4, atol=1e-5)
-    # the same key one position beyond the causal bound of a 2-token portion's first row is not seen by it
-    if where == Tk - 1:
-        q2 = torch.cat([q, q])
-        cu = torch.tensor([0, 2], dtype=torch.int32, device=DEV)
-        out2 = ops.latent_attn_paged(ctx, q2.to(DEV), cache, bt, cl, cu, 2, bs, 1.0)
-        assert torch.allclose(out2.cpu(), attn_want(q2, c, 1.0), rtol=1e-4, atol=1e-5)
-        assert not torch.allclose(out2[0, 0].cpu(), c[where], atol=1e-1)
+    c, q = c.to(dt).float(), q.to(dt).float()
+    t = dict(rtol=1e-4, atol=1e-5) if dt == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    cache, bt, cl = paged([c], bs, 16, dt, 16)
+    out = ops.latent_attn_paged(ctx, q.to(dt).to(DEV), cache, bt, cl, None, 1, bs, 1.0)
+    assert torch.allclose(out[0, 0].float().cpu(), c[where], atol=1e-3 if dt == torch.float32 else 3e-2)
+    assert torch.allclose(out.float().cpu(), attn_want(q, c, 1.0), **t)
+    # a portion of 40 tokens ends the sequence: row i sees the key iff where <= 661 + i
+    q40 = q.repeat(40, 1, 1)
+    cu = torch.tensor([0, 40], dtype=torch.int32, device=DEV)
+    out40 = ops.latent_attn_paged(ctx, q40.to(dt).to(DEV), cache, bt, cl, cu, 40, bs, 1.0)
+    assert torch.allclose(out40.float().cpu(), attn_want(q40, c, 1.0), **t)
+    for i in (0, 38, 39):
+        sees = where <= Tk - 40 + i
+        assert torch.allclose(out40[i, 0].float().cpu(), c[where], atol=1e-1) == sees
