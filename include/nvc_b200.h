@@ -303,7 +303,8 @@ int nvc_latent_norm_store(nvc_ctx* ctx, const float* in, int ldi, int n0, int of
 /* kind NVC_ACT_GELU_TANH_MUL: out[n, j] = gelu_tanh(in[n, j]) * in[n, Fp + j];  NVC_ACT_RELU2: out[n, j] = max(in[n, j], 0)^2;
  * j < F.  in and out may alias for NVC_ACT_RELU2. */
 int nvc_act_mul(nvc_ctx* ctx, const void* in, int ldi, void* out, int ldo, int dtype, int N, int F, int Fp, int kind, void* stream);
-/* C[b] = act(A[b] . W[b]^T) on the fp32 FMA pipe, any sizes: A [M, K] (+ b * sa), W [N, K] (+ b * sw), C [M, N] (+ b * sc),
+/* C[b] = act(A[b] . W[b]^T), any sizes (fp32 operands: FMA pipe, plain IEEE; bf16 operands with 16-byte-aligned rows - lda,
+ * ldw, sa, sw, K multiples of 8 - tensor pipe with fp32 accumulators, other bf16 shapes: FMA pipe): A [M, K] (+ b * sa), W [N, K] (+ b * sw), C [M, N] (+ b * sc),
  * b < batch.  in_dtype: A and W; out_dtype: C (fp32 operands give fp32).  act: NVC_ACT_NONE or NVC_ACT_RELU2. */
 int nvc_linear(nvc_ctx* ctx, const void* A, int lda, int64_t sa, const void* W, int ldw, int64_t sw, void* C, int ldc, int64_t sc,
                int in_dtype, int out_dtype, int M, int N, int K, int batch, int act, void* stream);

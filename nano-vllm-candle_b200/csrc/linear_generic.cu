@@ -1,11 +1,15 @@
-// C = act(A . W^T) for any sizes and both storage formats, on the fp32 FMA pipe (plain IEEE products and sums:
-// this is the matrix product of the exact fp32 mode, and of bf16 shapes the tcgen05 kernels do not take).
-// Three forms share one kernel:
+// C = act(A . W^T) for any sizes and both storage formats.  fp32 operands run on the FMA pipe (plain IEEE products and
+// sums: the matrix product of the exact mode); bf16 operands whose rows are 16-byte aligned run on the tensor pipe
+// (mma.sync m16n8k16, fp32 accumulators, cp.async double buffering) - the small per-head and per-expert products that the
+// tcgen05 GEMMs (one dense product per launch, K % 64) do not take.
+// Three forms share each kernel:
 //   plain      C[M, N] = A[M, K] . W[N, K]^T
 //   batched    blockIdx.z = b: A + b * sa, W + b * sw, C + b * sc  (one small product per attention head)
 //   grouped    rows [offsets[g], offsets[g + 1]) of C use W + g * sw; row r of A is a_rows[r] (mixture of experts:
 //              the rows of one expert are contiguous after the sort, offsets live in device memory)
 // 64 x 64 output tile per CTA, 16-deep k-slices through shared memory, 4 x 4 outputs per thread.
+#include <cstdlib>
+
 #include "typed.cuh"
 
 namespace {
@@ -87,6 +91,144 @@ linear_kernel(const T* __restrict__ A, int lda, int64_t sa, const int32_t* __res
   }
 }
 
+// ---- bf16 on the tensor pipe: 64 x 64 tile, 4 warps of 32 x 32, k-slices of 32 --------------------------------------
+constexpr int MK = 32;                 // k per stage
+constexpr int MROW = (MK + 8) * 2;     // bytes per padded smem row (80: the 8 rows of an ldmatrix hit 8 different 16-byte segments)
+
+__device__ __forceinline__ void cp16(uint32_t dst, const void* src, uint32_t bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void ldsm4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <typename TC>
+__global__ void __launch_bounds__(128)
+linear_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, int64_t sa, const int32_t* __restrict__ a_rows,
+                  const __nv_bfloat16* __restrict__ W, int ldw, int64_t sw, TC* __restrict__ C, int ldc, int64_t sc,
+                  const int32_t* __restrict__ offsets, int groups, int M, int N, int K, int act) {
+  __shared__ __align__(128) uint8_t sA[2][TM * MROW];
+  __shared__ __align__(128) uint8_t sW[2][TN * MROW];
+  pdl_trigger();
+  pdl_wait();
+  int row0, row_end;
+  if (offsets) {
+    int t = blockIdx.x, g = 0, base = 0;
+    for (; g < groups; ++g) {
+      base = offsets[g];
+      const int tiles = (offsets[g + 1] - base + TM - 1) / TM;
+      if (t < tiles) break;
+      t -= tiles;
+    }
+    if (g == groups) return;
+    row0 = base + t * TM;
+    row_end = offsets[g + 1];
+    W += (int64_t)g * sw;
+  } else {
+    row0 = blockIdx.x * TM;
+    row_end = M;
+    A += (int64_t)blockIdx.z * sa;
+    W += (int64_t)blockIdx.z * sw;
+    C += (int64_t)blockIdx.z * sc;
+  }
+  const int col0 = blockIdx.y * TN;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
+  // loader: 64 rows x 4 chunks of 16 bytes per operand and stage; thread -> rows (tid / 4) and (tid / 4 + 32), chunk tid % 4
+  const int lc = tid & 3;
+  const __nv_bfloat16* a_src[2];
+  const __nv_bfloat16* w_src[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = (tid >> 2) + 32 * i;
+    const int ar = row0 + r;
+    a_src[i] = ar < row_end ? A + (int64_t)(a_rows ? a_rows[ar] : ar) * lda : nullptr;
+    w_src[i] = col0 + r < N ? W + (int64_t)(col0 + r) * ldw : nullptr;
+  }
+  auto load = [&](int kb, int stage) {
+    const int k = kb * MK + lc * 8;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int r = (tid >> 2) + 32 * i;
+      const uint32_t off = r * MROW + lc * 16;
+      // K is a multiple of 8: a chunk is inside the row or entirely past its end (zero-filled)
+      cp16(smem_u32(sA[stage]) + off, a_src[i] && k < K ? (const void*)(a_src[i] + k) : (const void*)A, a_src[i] && k < K ? 16u : 0u);
+      cp16(smem_u32(sW[stage]) + off, w_src[i] && k < K ? (const void*)(w_src[i] + k) : (const void*)W, w_src[i] && k < K ? 16u : 0u);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  float acc[2][4][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
+  const int nkb = (K + MK - 1) / MK;
+  load(0, 0);
+  for (int kb = 0; kb < nkb; ++kb) {
+    if (kb + 1 < nkb) load(kb + 1, (kb + 1) & 1);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    __syncthreads();
+    const uint32_t a_base = smem_u32(sA[kb & 1]), w_base = smem_u32(sW[kb & 1]);
+#pragma unroll
+    for (int ks = 0; ks < MK / 16; ++ks) {
+      uint32_t af[2][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+        ldsm4(a_base + (wm + mt * 16 + (lane & 15)) * MROW + (ks * 2 + (lane >> 4)) * 16, af[mt][0], af[mt][1], af[mt][2], af[mt][3]);
+#pragma unroll
+      for (int np = 0; np < 2; ++np) {
+        uint32_t b0, b1, b2, b3;
+        ldsm4(w_base + (wn + np * 16 + (lane & 7) + ((lane >> 4) << 3)) * MROW + (ks * 2 + ((lane >> 3) & 1)) * 16, b0, b1, b2, b3);
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+          mma16816(acc[mt][2 * np], af[mt], b0, b1);
+          mma16816(acc[mt][2 * np + 1], af[mt], b2, b3);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  const int quad = lane >> 2, tq = lane & 3;
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int r = row0 + wm + mt * 16 + quad + 8 * hf;
+      if (r >= row_end) continue;
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int c = col0 + wn + nt * 8 + 2 * tq + e;
+          if (c >= N) continue;
+          float v = acc[mt][nt][2 * hf + e];
+          if (act == NVC_ACT_RELU2) { v = fmaxf(v, 0.f); v *= v; }
+          st_f(C + (int64_t)r * ldc + c, v);
+        }
+    }
+}
+
+bool mma_ok(int in_dtype, const void* A, int lda, int64_t sa, const void* W, int ldw, int64_t sw, int K) {
+  static const bool env = !(getenv("NVC_LINEAR_MMA") && atoi(getenv("NVC_LINEAR_MMA")) == 0);
+  return env && in_dtype == NVC_DT_BF16 && K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && sa % 8 == 0 && sw % 8 == 0 &&
+         ((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0;
+}
+
+template <typename TC>
+int launch_mma(nvc_ctx* ctx, dim3 grid, void* stream, const void* A, int lda, int64_t sa, const int32_t* a_rows, const void* W, int ldw,
+               int64_t sw, void* C, int ldc, int64_t sc, const int32_t* offsets, int groups, int M, int N, int K, int act) {
+  NVC_CUDA_CHECK(ctx, nvc_launch(ctx, linear_mma_kernel<TC>, grid, dim3(128), 0, nvc_stream(stream),
+                                 reinterpret_cast<const __nv_bfloat16*>(A), lda, sa, a_rows, reinterpret_cast<const __nv_bfloat16*>(W), ldw,
+                                 sw, reinterpret_cast<TC*>(C), ldc, sc, offsets, groups, M, N, K, act));
+  ctx->launches++;
+  return NVC_OK;
+}
+
 template <typename T, typename TC>
 int launch(nvc_ctx* ctx, dim3 grid, void* stream, const void* A, int lda, int64_t sa, const int32_t* a_rows, const void* W, int ldw,
            int64_t sw, void* C, int ldc, int64_t sc, const int32_t* offsets, int groups, int M, int N, int K, int act) {
@@ -100,6 +242,11 @@ int launch(nvc_ctx* ctx, dim3 grid, void* stream, const void* A, int lda, int64_
 int dispatch(nvc_ctx* ctx, dim3 grid, void* stream, int in_dtype, int out_dtype, const void* A, int lda, int64_t sa,
              const int32_t* a_rows, const void* W, int ldw, int64_t sw, void* C, int ldc, int64_t sc, const int32_t* offsets,
              int groups, int M, int N, int K, int act) {
+  if (mma_ok(in_dtype, A, lda, sa, W, ldw, sw, K)) {
+    if (out_dtype == NVC_DT_F32)
+      return launch_mma<float>(ctx, grid, stream, A, lda, sa, a_rows, W, ldw, sw, C, ldc, sc, offsets, groups, M, N, K, act);
+    return launch_mma<__nv_bfloat16>(ctx, grid, stream, A, lda, sa, a_rows, W, ldw, sw, C, ldc, sc, offsets, groups, M, N, K, act);
+  }
   if (in_dtype == NVC_DT_F32) {
     NVC_REQUIRE(ctx, out_dtype == NVC_DT_F32, NVC_EINVAL, "fp32 operands give an fp32 result");
     return launch<float, float>(ctx, grid, stream, A, lda, sa, a_rows, W, ldw, sw, C, ldc, sc, offsets, groups, M, N, K, act);

@@ -83,7 +83,7 @@ def test_activations(ctx, ops, dt):
 
 
 @pytest.mark.parametrize("dt", DTS)
-@pytest.mark.parametrize("shape", [(1, 16, 8), (70, 130, 100), (5, 257, 33), (200, 64, 64)])
+@pytest.mark.parametrize("shape", [(1, 16, 8), (70, 130, 100), (5, 257, 33), (200, 64, 64), (130, 72, 40), (64, 200, 264)])
 def test_linear_any_shape(ctx, ops, dt, shape):
     M, N, Kd = shape
     g = torch.Generator().manual_seed(5)
