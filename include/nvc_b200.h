@@ -179,6 +179,12 @@ int nvc_gemm_bf16(nvc_ctx* ctx, const nvc_bf16* A, int lda, const nvc_bf16* W, v
 int nvc_gemm_bf16_silu_mul(nvc_ctx* ctx, const nvc_bf16* A, int lda, const nvc_bf16* W_gu16, nvc_bf16* act,
                            int ldc, int M, int I, int K, void* stream);
 
+/* The same fused kernel with the tanh form of gelu on the gate (gated feed-forward of the Karuzen family):
+ *   act[M, I] = gelu_tanh(A Wgate^T) * (A Wup^T),  gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))),
+ * hardware tanh on the fp32 accumulators; W_gu16 interleaved as for nvc_gemm_bf16_silu_mul. */
+int nvc_gemm_bf16_gelu_mul(nvc_ctx* ctx, const nvc_bf16* A, int lda, const nvc_bf16* W_gu16, nvc_bf16* act,
+                           int ldc, int M, int I, int K, void* stream);
+
 /* Host-side rope table: replaces RotaryEmbedding::build_cos_sin
  * (src/layers/rotary_embedding.rs:56-80), which the reference recomputes per call.
  * out: f32 [max_pos, head_dim]; row p = [cos(p*f_0..f_{hd/2-1}), sin(p*f_0..)], with

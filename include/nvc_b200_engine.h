@@ -102,6 +102,10 @@ int nvc_runner_set_logit_rows(nvc_runner* r, const int32_t* rows, int n);
 /* Debug tap: the next step copies the fp32 residual stream after every layer run into host memory,
  * [layer runs, N, width]; host == NULL disarms. */
 int nvc_runner_set_residual_tap(nvc_runner* r, float* host, int64_t capacity_floats);
+/* Per-op timing of a registry model: the next prefill / mixed step (not a graph-replayed decode step) records CUDA events
+ * around every op; nvc_runner_profile_json then returns {"op": microseconds summed over the layer runs, ...} of that step. */
+int nvc_runner_arm_profile(nvc_runner* r);
+const char* nvc_runner_profile_json(const nvc_runner* r);
 int nvc_runner_layer_runs(const nvc_runner* r);
 int nvc_runner_width(const nvc_runner* r);
 

@@ -72,6 +72,7 @@ def declare(l: C.CDLL) -> None:
         "nvc_runner_set_logit_rows": [_vp, _vp, _i],
         "nvc_runner_set_residual_tap": [_vp, _vp, _i64],
         "nvc_runner_layer_runs": [_vp],
+        "nvc_runner_arm_profile": [_vp],
         "nvc_runner_width": [_vp],
         "nvc_engine_step_forced": [_vp, _i, _vp, _vp, _vp, _vp, _vp, C.POINTER(StepOutputC)],
         "nvc_engine_close_request": [_vp, _i64],
@@ -107,6 +108,8 @@ def declare(l: C.CDLL) -> None:
     l.nvc_model_config_architecture.restype = C.c_char_p
     l.nvc_model_config_last_error.argtypes = []
     l.nvc_model_config_last_error.restype = C.c_char_p
+    l.nvc_runner_profile_json.argtypes = [_vp]
+    l.nvc_runner_profile_json.restype = C.c_char_p
     l.nvc_hf_last_error.argtypes = []
     l.nvc_hf_last_error.restype = C.c_char_p
     l.nvc_hf_last_warning.argtypes = []

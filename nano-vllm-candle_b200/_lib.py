@@ -77,6 +77,7 @@ def _declare(l: C.CDLL) -> None:
         "nvc_gemm_bf16": [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp],
         "nvc_gemm_bf16_ex": [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
         "nvc_gemm_bf16_silu_mul": [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp],
+        "nvc_gemm_bf16_gelu_mul": [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp],
         "nvc_gemm_bf16_silu_mul_ex": [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
         "nvc_gemm_bf16_trace": [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
         "nvc_rope_table_init_sync": [_vp, _f, _i, _i, _vp],

@@ -11,7 +11,29 @@
 // NVC_EPI_TRANSPOSE (pair kernel, persistent schedule): the operands are swapped by the host - the kernel's "A" rows are
 // weight rows, its "W" rows are tokens - and the epilogue stores its accumulator row r as COLUMN r of C: lm_head at decode
 // batch sizes, where 64 tokens would fill a quarter of a 256-row MMA and only one CTA of the pair would hold valid rows.
-enum { NVC_EPI_NONE = 0, NVC_EPI_SILU_MUL = 1, NVC_EPI_TRANSPOSE = 2, NVC_EPI_QK_NORM_ROPE = 3 };
+enum { NVC_EPI_NONE = 0, NVC_EPI_SILU_MUL = 1, NVC_EPI_TRANSPOSE = 2, NVC_EPI_QK_NORM_ROPE = 3, NVC_EPI_GELU_TANH_MUL = 4 };
+
+// the gated epilogues write half as many columns as the accumulator has
+__host__ __device__ __forceinline__ bool nvc_epi_gated(int epi) { return epi == NVC_EPI_SILU_MUL || epi == NVC_EPI_GELU_TANH_MUL; }
+
+#ifdef __CUDACC__
+// act(gate) * up for 16 features; silu with the fast reciprocal, tanh-gelu with the hardware tanh (both far inside the
+// bf16 rounding of the result)
+__device__ __forceinline__ void nvc_gated16(int epi, const float* f, float* o) {
+  if (epi == NVC_EPI_SILU_MUL) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) o[j] = __fdividef(f[j], 1.0f + __expf(-f[j])) * f[16 + j];
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float z = f[j];
+      float t;
+      asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+      o[j] = 0.5f * z * (1.0f + t) * f[16 + j];
+    }
+  }
+}
+#endif
 
 struct QkEpi {
   const uint4* qw = nullptr;         // q_norm weight [128] bf16
@@ -45,13 +67,12 @@ __device__ __forceinline__ void store16(void* C, int out_f32, int64_t off, const
 //                    C[row, n0/2 .. n0/2+16) = silu(gate) * up   (src/layers/activation.rs:13-18,
 //                    silu(x) = x / (1 + exp(-x)) in f32), bf16.  row_off = row * ldc in elements of C.
 __device__ __forceinline__ void emit32(void* C, int out_f32, int epi, int64_t row_off, int n0, int N, const float* f) {
-  if (epi == NVC_EPI_SILU_MUL) {
+  if (nvc_epi_gated(epi)) {
     if (n0 < N) {
       float o[16];
-#pragma unroll
       // fast reciprocal (MUFU.RCP, 2 ulp): an IEEE division per element makes the epilogue of a K = 1024
       // prefill tile (128 of them per thread) as long as its main loop
-      for (int j = 0; j < 16; ++j) o[j] = __fdividef(f[j], 1.0f + __expf(-f[j])) * f[16 + j];
+      nvc_gated16(epi, f, o);
       store16(C, 0, row_off + (n0 >> 1), o);
     }
   } else {
@@ -99,10 +120,9 @@ struct RowStage {
   }
   // 32 consecutive accumulator columns of this thread's row (same semantics as emit32); flushes every 128 bytes
   __device__ __forceinline__ void emit32(int lane, int out_f32, int epi, const float* f) {
-    if (epi == NVC_EPI_SILU_MUL) {
+    if (nvc_epi_gated(epi)) {
       float o[16];
-#pragma unroll
-      for (int j = 0; j < 16; ++j) o[j] = __fdividef(f[j], 1.0f + __expf(-f[j])) * f[16 + j];
+      nvc_gated16(epi, f, o);
       put(lane, pack8(o));
       put(lane, pack8(o + 8));
     } else if (out_f32) {
@@ -125,9 +145,9 @@ __device__ __forceinline__ RowStage make_row_stage(uint8_t* buf, void* C, int ou
                                                    int n_base, int n_tile_cols, int N) {
   // SiLU-mul: 32 accumulator columns -> 16 bf16; plain: bf16 or f32 per column
   const int esz = out_f32 ? 4 : 2;
-  const int col0 = epi == NVC_EPI_SILU_MUL ? (n_base >> 1) : n_base;
-  const int n_out = epi == NVC_EPI_SILU_MUL ? (N >> 1) : N;
-  const int tile_out = epi == NVC_EPI_SILU_MUL ? (n_tile_cols >> 1) : n_tile_cols;
+  const int col0 = nvc_epi_gated(epi) ? (n_base >> 1) : n_base;
+  const int n_out = nvc_epi_gated(epi) ? (N >> 1) : N;
+  const int tile_out = nvc_epi_gated(epi) ? (n_tile_cols >> 1) : n_tile_cols;
   RowStage s;
   s.buf = buf;
   s.g_row0 = reinterpret_cast<uint8_t*>(C) + ((int64_t)row0 * ldc + col0) * esz;

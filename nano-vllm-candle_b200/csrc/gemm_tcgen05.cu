@@ -529,9 +529,9 @@ static int gemm_impl(nvc_ctx* ctx, const nvc_bf16* A, int lda, const nvc_bf16* W
   NVC_REQUIRE(ctx, K % 64 == 0, NVC_ESHAPE, "K must be a multiple of 64");
   NVC_REQUIRE(ctx, Nout % 16 == 0, NVC_ESHAPE, "Nout must be a multiple of 16");
   NVC_REQUIRE(ctx, lda % 8 == 0 && lda >= K, NVC_ESHAPE, "lda must be >= K and a multiple of 8");
-  NVC_REQUIRE(ctx, ldc >= (epi == NVC_EPI_SILU_MUL ? Nout / 2 : Nout) && ldc % 8 == 0, NVC_ESHAPE,
+  NVC_REQUIRE(ctx, ldc >= (nvc_epi_gated(epi) ? Nout / 2 : Nout) && ldc % 8 == 0, NVC_ESHAPE,
               "ldc must be >= the output width and a multiple of 8");
-  NVC_REQUIRE(ctx, epi == NVC_EPI_NONE || (epi == NVC_EPI_SILU_MUL && Nout % 32 == 0 && out_dtype == NVC_DT_BF16),
+  NVC_REQUIRE(ctx, epi == NVC_EPI_NONE || (nvc_epi_gated(epi) && Nout % 32 == 0 && out_dtype == NVC_DT_BF16),
               NVC_ESHAPE, "fused SiLU-mul epilogue needs Nout % 32 == 0 and bf16 output");
   NVC_REQUIRE(ctx, out_dtype == NVC_DT_BF16 || out_dtype == NVC_DT_F32, NVC_EINVAL, "bad out_dtype");
   NVC_REQUIRE(ctx, ((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0 && ((uintptr_t)C % 16) == 0, NVC_EINVAL,
@@ -619,6 +619,13 @@ extern "C" int nvc_gemm_bf16_silu_mul_ex(nvc_ctx* ctx, const nvc_bf16* A, int ld
   NVC_REQUIRE(ctx, I > 0 && I % 16 == 0, NVC_ESHAPE, "I must be a multiple of 16");
   return gemm_impl(ctx, A, lda, W_gu16, act, ldc, NVC_DT_BF16, M, 2 * I, K, force_bn, force_splits, NVC_EPI_SILU_MUL,
                    stream, nullptr);
+}
+
+// The same fused kernel with the tanh form of gelu on the gate: act = gelu_tanh(A Wg^T) * (A Wu^T).
+extern "C" int nvc_gemm_bf16_gelu_mul(nvc_ctx* ctx, const nvc_bf16* A, int lda, const nvc_bf16* W_gu16, nvc_bf16* act, int ldc, int M,
+                                      int I, int K, void* stream) {
+  NVC_REQUIRE(ctx, I > 0 && I % 16 == 0, NVC_ESHAPE, "I must be a multiple of 16");
+  return gemm_impl(ctx, A, lda, W_gu16, act, ldc, NVC_DT_BF16, M, 2 * I, K, 0, 0, NVC_EPI_GELU_TANH_MUL, stream, nullptr);
 }
 
 extern "C" int nvc_gemm_bf16_silu_mul(nvc_ctx* ctx, const nvc_bf16* A, int lda, const nvc_bf16* W_gu16, nvc_bf16* act,

@@ -77,13 +77,16 @@ latent_attn_mma_kernel(const nvc_bf16* __restrict__ q, int ldq, const nvc_bf16* 
         // 32 lanes cover 16 rows x NC chunks in 16 * NC / 32 rounds
         constexpr int kRowsPerRound = 32 / NC;       // NC = 8: 4 rows per round; NC = 16: 2 rows
         const int c = lane % NC;
+        // tiles start at multiples of 16: with a block size that is a multiple of 16 a tile lies in one block
+        const bool one_block = (block_size & 15) == 0;
+        const int64_t slot0 = (int64_t)__ldg(bt + tok0 / block_size) * block_size + tok0 % block_size;
 #pragma unroll
         for (int rr = 0; rr < 16 / kRowsPerRound; ++rr) {
           const int r = rr * kRowsPerRound + lane / NC;
           const int tok = tok0 + r;
           const uint32_t ok = tok <= kmax ? 16u : 0u;
           const int tk = ok ? tok : tok0;
-          const int64_t slot = (int64_t)__ldg(bt + tk / block_size) * block_size + tk % block_size;
+          const int64_t slot = one_block ? slot0 + (tk - tok0) : (int64_t)__ldg(bt + tk / block_size) * block_size + tk % block_size;
           cp_async16(st + r * RB + ((c ^ (r & 7)) << 4), reinterpret_cast<const uint8_t*>(cache + slot * ldc) + c * 16, ok);
         }
       }

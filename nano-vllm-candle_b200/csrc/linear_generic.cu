@@ -201,15 +201,19 @@ linear_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, int64_t sa, cons
       const int r = row0 + wm + mt * 16 + quad + 8 * hf;
       if (r >= row_end) continue;
 #pragma unroll
-      for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int c = col0 + wn + nt * 8 + 2 * tq + e;
-          if (c >= N) continue;
-          float v = acc[mt][nt][2 * hf + e];
-          if (act == NVC_ACT_RELU2) { v = fmaxf(v, 0.f); v *= v; }
-          st_f(C + (int64_t)r * ldc + c, v);
+      for (int nt = 0; nt < 4; ++nt) {
+        const int c = col0 + wn + nt * 8 + 2 * tq;
+        float v0 = acc[mt][nt][2 * hf], v1 = acc[mt][nt][2 * hf + 1];
+        if (act == NVC_ACT_RELU2) { v0 = fmaxf(v0, 0.f); v0 *= v0; v1 = fmaxf(v1, 0.f); v1 *= v1; }
+        TC* dst = C + (int64_t)r * ldc + c;
+        if (c + 1 < N && (reinterpret_cast<uintptr_t>(dst) % (2 * sizeof(TC))) == 0) {     // the pair in one store
+          if constexpr (sizeof(TC) == 2) *reinterpret_cast<uint32_t*>(dst) = pack_bf16(v0, v1);
+          else *reinterpret_cast<float2*>(dst) = make_float2(v0, v1);
+        } else {
+          if (c < N) st_f(dst, v0);
+          if (c + 1 < N) st_f(dst + 1, v1);
         }
+      }
     }
 }
 

@@ -92,6 +92,40 @@ struct KaruzenBody : nvc_model_body {
   float *tk_w = nullptr, *gate = nullptr;
   float* tap_host = nullptr;
   size_t tap_cap = 0;
+  bool prof_armed = false, prof_on = false;
+  std::vector<std::pair<const char*, cudaEvent_t>> marks;
+  std::string prof_json = "{}";
+
+  int arm_profile() override { prof_armed = true; return NVC_OK; }
+  bool profile_armed() const override { return prof_armed; }
+  const char* profile_json() const override { return prof_json.c_str(); }
+  // names the op(s) launched since the previous mark
+  void mark(nvc_runner* r, const char* name) {
+    if (!prof_on) return;
+    cudaEvent_t e;
+    if (cudaEventCreate(&e) != cudaSuccess) return;
+    cudaEventRecord(e, r->stream);
+    marks.emplace_back(name, e);
+  }
+  void finish_profile(nvc_runner* r) {
+    if (!prof_on) return;
+    prof_on = false;
+    cudaStreamSynchronize(r->stream);
+    std::map<std::string, double> us;
+    std::vector<std::string> order;
+    for (size_t i = 1; i < marks.size(); ++i) {
+      float ms = 0.f;
+      cudaEventElapsedTime(&ms, marks[i - 1].second, marks[i].second);
+      if (!us.count(marks[i].first)) order.push_back(marks[i].first);
+      us[marks[i].first] += ms * 1e3;
+    }
+    for (auto& m : marks) cudaEventDestroy(m.second);
+    marks.clear();
+    prof_json = "{";
+    for (size_t i = 0; i < order.size(); ++i)
+      prof_json += (i ? ", \"" : "\"") + order[i] + "\": " + std::to_string(us[order[i]]);
+    prof_json += "}";
+  }
 
   int vocab() const override { return cfg.vocab; }
   int logits_ld() const override { return Vp; }
@@ -301,8 +335,16 @@ struct KaruzenBody : nvc_model_body {
         for (int hh = 0; hh < m.heads && !rc; ++hh)
           rc = put_matrix(r, w.w_o, (size_t)m.heads * w.vdp, 0, (size_t)hh * w.vdp, v.data() + (size_t)hh * m.vdim, W, m.vdim,
                           (size_t)m.heads * m.vdim, 1);
-      } else if (sub == "mlp.gate") { if (!shape_is(f.ff, W)) return bad(); rc = put_matrix(r, w.w_gu, Wp, 0, 0, v.data(), f.ff, W, W, 1); }
-      else if (sub == "mlp.up") { if (!shape_is(f.ff, W)) return bad(); rc = put_matrix(r, w.w_gu, Wp, w.ffp, 0, v.data(), f.ff, W, W, 1); }
+      } else if (sub == "mlp.gate" || sub == "mlp.up") {
+        if (!shape_is(f.ff, W)) return bad();
+        const bool up = sub == "mlp.up";
+        if (!use_tc) {                   // [gate rows; up rows at ffp]: two halves for the stand-alone activation kernel
+          rc = put_matrix(r, w.w_gu, Wp, up ? w.ffp : 0, 0, v.data(), f.ff, W, W, 1);
+        } else {                         // groups of 16 rows, gate group then up group: the fused epilogue meets both in one thread
+          for (int g0 = 0; g0 < f.ff && !rc; g0 += 16)
+            rc = put_matrix(r, w.w_gu, Wp, (size_t)2 * g0 + (up ? 16 : 0), 0, v.data() + (size_t)g0 * W, std::min(16, f.ff - g0), W, W, 1);
+        }
+      }
       else if (sub == "mlp.down") { if (!shape_is(W, f.ff)) return bad(); rc = put_matrix(r, w.w_fdown, w.ffp, 0, 0, v.data(), W, f.ff, f.ff, 1); }
       else if (sub == "mlp.router") { if (!shape_is(f.experts, W)) return bad(); rc = put_f32(r, w.router, v.data(), n); }
       else if (sub == "mlp.correction") { if (n != (size_t)f.experts) return bad(); rc = put_f32(r, w.corr, v.data(), n); }
@@ -356,8 +398,14 @@ struct KaruzenBody : nvc_model_body {
     void* st = r->stream;
     const int N = s.N, W = cfg.width;
     const int odt = dt;   // storage format of activations
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(r->stream, &cap);
+    prof_on = prof_armed && cap == cudaStreamCaptureStatusNone;
+    if (prof_on) prof_armed = false;
+    mark(r, "start");
     int rc = nvc_embed_gather_f32(ctx, r->d_ids, embed, dt, Wp, x0, Wp, N, W, st);
     if (rc) return rc;
+    mark(r, "embed");
     const float *a0 = nullptr, *a1 = nullptr;     // sums not yet added to the residual stream
     bool first = true;
     for (size_t k = 0; k < runs.size(); ++k) {
@@ -375,53 +423,77 @@ struct KaruzenBody : nvc_model_body {
                         nullptr, N, W, st);
       if (rc) return rc;
       first = false;
+      mark(r, "dyt_norm");
       // ---- mixer
       const int dl = w.qrp + w.kvp;
       if ((rc = linear(r, h, Wp, w.w_down, down, dl, NVC_DT_F32, N, dl, Wp))) return rc;
+      mark(r, "gemm_down_latents");
       if ((rc = nvc_latent_norm_store(ctx, down, dl, m.q_rank, w.qrp, m.kv_rank, w.dq_norm, w.dkv_norm, cfg.eps, cq, w.qrp, cache[k],
                                       w.kvp, r->d_slots, dt, N, st)))
         return rc;
+      mark(r, "latent_norm_store");
       const int qw = m.heads * w.dimp, lw = m.heads * w.kvp, vw = m.heads * w.vdp;
       if ((rc = linear(r, cq, w.qrp, w.w_uq, q, qw, odt, N, qw, w.qrp))) return rc;
+      mark(r, "gemm_uq");
       if ((rc = nvc_linear(ctx, q, qw, w.dimp, w.w_ukT, w.dimp, (int64_t)w.kvp * w.dimp, qabs, lw, w.kvp, dt, odt, N, w.kvp, w.dimp,
                            m.heads, NVC_ACT_NONE, st)))
         return rc;
+      mark(r, "absorb_uk");
       if ((rc = nvc_latent_attn_paged(ctx, qabs, lw, cache[k], w.kvp, r->d_bt, r->max_blocks_cap, r->d_ctx, s.decode ? nullptr : r->d_cu,
                                       s.B, s.decode ? 1 : s.max_seqlen, m.heads, m.kv_rank, w.kvp, r->opt.kvcache_block_size, m.scale,
                                       olat, lw, dt, st)))
         return rc;
+      mark(r, "latent_attn");
       if ((rc = nvc_linear(ctx, olat, lw, w.kvp, w.w_uv, w.kvp, (int64_t)w.vdp * w.kvp, ao, vw, w.vdp, dt, odt, N, w.vdp, w.kvp, m.heads,
                            NVC_ACT_NONE, st)))
         return rc;
+      mark(r, "absorb_uv");
       if ((rc = linear(r, ao, vw, w.w_o, mix, Wp, NVC_DT_F32, N, Wp, vw))) return rc;
+      mark(r, "gemm_o");
       a0 = mix;
       a1 = nullptr;
       // ---- feed-forward
       if (f.kind == nvc_karuzen_mlp::Dense) {
-        if ((rc = linear(r, h, Wp, w.w_gu, gu, 2 * w.ffp, odt, N, 2 * w.ffp, Wp))) return rc;
-        if ((rc = nvc_act_mul(ctx, gu, 2 * w.ffp, act, w.ffp, dt, N, f.ff, w.ffp, NVC_ACT_GELU_TANH_MUL, st))) return rc;
+        if (use_tc) {                    // gate_up projection with the gated gelu in the GEMM's epilogue
+          if ((rc = nvc_gemm_bf16_gelu_mul(ctx, reinterpret_cast<const nvc_bf16*>(h), Wp, reinterpret_cast<const nvc_bf16*>(w.w_gu),
+                                           reinterpret_cast<nvc_bf16*>(act), w.ffp, N, w.ffp, Wp, st)))
+            return rc;
+          mark(r, "gemm_gate_up");
+        } else {
+          if ((rc = linear(r, h, Wp, w.w_gu, gu, 2 * w.ffp, odt, N, 2 * w.ffp, Wp))) return rc;
+          mark(r, "gemm_gate_up");
+          if ((rc = nvc_act_mul(ctx, gu, 2 * w.ffp, act, w.ffp, dt, N, f.ff, w.ffp, NVC_ACT_GELU_TANH_MUL, st))) return rc;
+          mark(r, "gelu_mul");
+        }
         if ((rc = linear(r, act, w.ffp, w.w_fdown, ffo, Wp, NVC_DT_F32, N, Wp, w.ffp))) return rc;
+        mark(r, "gemm_ff_down");
         a1 = ffo;
       } else if (f.kind == nvc_karuzen_mlp::Moe) {
         const int P = N * f.top;
         if ((rc = nvc_moe_route(ctx, h, dt, Wp, w.router, w.corr, w.sg, f.experts, f.top, f.router_scale, tk_idx, tk_w, w.sg ? gate : nullptr,
                                 N, W, st)))
           return rc;
+        mark(r, "moe_route");
         if ((rc = nvc_moe_sort(ctx, tk_idx, N, f.top, f.experts, offsets, src_rows, pos, st))) return rc;
+        mark(r, "moe_sort");
         if ((rc = nvc_linear_grouped(ctx, h, Wp, src_rows, w.w_eup, Wp, (int64_t)w.effp * Wp, hid, w.effp, offsets, f.experts, P, dt, odt,
                                      w.effp, Wp, NVC_ACT_RELU2, st)))
           return rc;
+        mark(r, "moe_up");
         if ((rc = nvc_linear_grouped(ctx, hid, w.effp, nullptr, w.w_edown, w.effp, (int64_t)Wp * w.effp, y, Wp, offsets, f.experts, P, dt,
                                      NVC_DT_F32, Wp, w.effp, NVC_ACT_NONE, st)))
           return rc;
+        mark(r, "moe_down");
         if (w.w_sup) {
           if ((rc = linear(r, h, Wp, w.w_sup, su, w.sfp, odt, N, w.sfp, Wp))) return rc;
           if ((rc = nvc_act_mul(ctx, su, w.sfp, su, w.sfp, dt, N, f.shared_ff, w.sfp, NVC_ACT_RELU2, st))) return rc;
           if ((rc = linear(r, su, w.sfp, w.w_sdown, sd, Wp, NVC_DT_F32, N, Wp, w.sfp))) return rc;
+          mark(r, "shared_expert");
         }
         if ((rc = nvc_moe_combine(ctx, y, NVC_DT_F32, Wp, pos, tk_w, f.top, w.w_sup ? sd : nullptr, NVC_DT_F32, Wp, w.w_sup ? gate : nullptr,
                                   ffo, Wp, N, W, st)))
           return rc;
+        mark(r, "moe_combine");
         a1 = ffo;
       }
     }
@@ -434,7 +506,11 @@ struct KaruzenBody : nvc_model_body {
     // ---- head: final norm of the wanted rows (the last run's sums are added on the way), logits against the embedding
     rc = nvc_dyt_norm(ctx, res, a0, a1, nullptr, nullptr, Wp, fw, fb, falpha, hn, odt, Wp, s.decode ? nullptr : r->d_last_rows, s.rows, W, st);
     if (rc) return rc;
-    return linear(r, hn, Wp, embed, r->logits, Vp, NVC_DT_F32, s.rows, Vp, Wp);
+    mark(r, "final_norm");
+    rc = linear(r, hn, Wp, embed, r->logits, Vp, NVC_DT_F32, s.rows, Vp, Wp);
+    mark(r, "lm_head");
+    finish_profile(r);
+    return rc;
   }
 };
 

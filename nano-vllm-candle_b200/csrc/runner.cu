@@ -761,7 +761,7 @@ extern "C" int nvc_runner_decode(nvc_runner* r, const int32_t* ids, const int32_
     return enqueue_token_readback(r, B);
   };
   int rc = NVC_OK;
-  if (r->opt.use_cuda_graph) {
+  if (r->opt.use_cuda_graph && !(r->body && r->body->profile_armed())) {   // a profiled step records events: not capturable
     const auto key = std::make_pair(B, key2);
     auto it = r->graphs.find(key);
     if (it == r->graphs.end()) {
@@ -1051,3 +1051,10 @@ extern "C" int nvc_runner_set_residual_tap(nvc_runner* r, float* host, int64_t c
 }
 extern "C" int nvc_runner_layer_runs(const nvc_runner* r) { return r && r->body ? r->body->layer_runs() : 0; }
 extern "C" int nvc_runner_width(const nvc_runner* r) { return !r ? 0 : (r->body ? r->body->width() : r->cfg.hidden_size); }
+
+extern "C" int nvc_runner_arm_profile(nvc_runner* r) {
+  if (!r) return NVC_EINVAL;
+  NVC_REQUIRE(r->ctx, r->body, NVC_ENOTIMPL, "per-op profiling of a step needs a registry model (Qwen3: nvc_runner_time_op)");
+  return r->body->arm_profile();
+}
+extern "C" const char* nvc_runner_profile_json(const nvc_runner* r) { return r && r->body ? r->body->profile_json() : "{}"; }

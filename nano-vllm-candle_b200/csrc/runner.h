@@ -37,6 +37,11 @@ struct nvc_model_body {
   virtual int logits_ld() const = 0;
   // optional: residual stream after every layer run of the next step, [runs, N, width] fp32 into host memory
   virtual int set_residual_tap(float* /*host*/, size_t /*capacity_floats*/) { return NVC_ENOTIMPL; }
+  // optional: the next (non-graph) step records CUDA events around every op; profile_json() = {"op": microseconds summed
+  // over layer runs, ...} of that step
+  virtual int arm_profile() { return NVC_ENOTIMPL; }
+  virtual bool profile_armed() const { return false; }
+  virtual const char* profile_json() const { return "{}"; }
   virtual int layer_runs() const { return 0; }
   virtual int width() const { return 0; }
 };

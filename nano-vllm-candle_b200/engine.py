@@ -445,6 +445,14 @@ class ModelRunner(Qwen3ModelRunner):
         check(self.l.nvc_runner_last_logits(self.handle, _p(out), B), "nvc_runner_last_logits", self.ctx.h)
         return out
 
+    def arm_profile(self) -> None:
+        """The next prefill / mixed step records CUDA events around every op (see profile())."""
+        check(self.l.nvc_runner_arm_profile(self.handle), "nvc_runner_arm_profile", self.ctx.h)
+
+    def profile(self) -> Dict[str, float]:
+        """{op: microseconds summed over the layer runs} of the last profiled step."""
+        return json.loads(self.l.nvc_runner_profile_json(self.handle).decode())
+
     def tap_residual(self, num_tokens: int) -> np.ndarray:
         """Arms the debug tap for the next step; the returned array [layer runs, tokens, width] is filled by that step."""
         runs, width = self.l.nvc_runner_layer_runs(self.handle), self.l.nvc_runner_width(self.handle)

@@ -182,6 +182,17 @@ class Context:
                                                   M, I, K, force_bn, force_splits, _stream()), "nvc_gemm_bf16_silu_mul")
         return out
 
+    def gemm_gelu_mul(self, a: torch.Tensor, w_gu16: torch.Tensor):
+        """act = gelu_tanh(a @ Wgate.T) * (a @ Wup.T); w_gu16 = interleave_gate_up([gate; up])."""
+        _req(a, BF16, "a"); _req(w_gu16, BF16, "w_gu16")
+        M, K = a.shape
+        I = w_gu16.shape[0] // 2
+        assert w_gu16.shape[1] == K and w_gu16.is_contiguous() and a.stride(1) == 1
+        out = torch.empty((M, I), dtype=BF16, device=a.device)
+        self._ck(self.l.nvc_gemm_bf16_gelu_mul(self.h, _ptr(a), a.stride(0), _ptr(w_gu16), _ptr(out), out.stride(0), M, I, K, _stream()),
+                 "nvc_gemm_bf16_gelu_mul")
+        return out
+
     def rope_table(self, theta: float, head_dim: int, max_pos: int, device=None):
         dev = torch.device("cuda", self.device) if device is None else device
         tab = torch.empty((max_pos, head_dim), dtype=torch.float32, device=dev)

@@ -82,6 +82,18 @@ def test_activations(ctx, ops, dt):
     assert torch.allclose(out.float().cpu(), torch.relu(xf) ** 2, **tol(dt))
 
 
+@pytest.mark.parametrize("M,I,Kd", [(1, 64, 64), (64, 192, 128), (300, 320, 192), (2100, 1024, 256)])
+def test_gate_up_projection_with_gelu_in_the_epilogue(ctx, ops, M, I, Kd):
+    """Both tcgen05 schedules (1-CTA tiles up to 128 rows, CTA pairs above) against gelu_tanh(gate) * up in fp32."""
+    g = torch.Generator().manual_seed(21)
+    a = torch.randn(M, Kd, generator=g).bfloat16()
+    w = (torch.randn(2 * I, Kd, generator=g) * Kd ** -0.5 * 2).bfloat16()
+    out = ctx.gemm_gelu_mul(a.to(DEV), ctx.interleave_gate_up(w.to(DEV)))
+    z = a.float() @ w.float().T
+    want = K.gelu_tanh(z[:, :I]) * z[:, I:]
+    assert torch.allclose(out.float().cpu(), want, rtol=2e-2, atol=2e-2)
+
+
 @pytest.mark.parametrize("dt", DTS)
 @pytest.mark.parametrize("shape", [(1, 16, 8), (70, 130, 100), (5, 257, 33), (200, 64, 64), (130, 72, 40), (64, 200, 264)])
 def test_linear_any_shape(ctx, ops, dt, shape):
