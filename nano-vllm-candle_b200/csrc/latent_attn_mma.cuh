@@ -47,10 +47,17 @@ latent_attn_mma_kernel(const nvc_bf16* __restrict__ q, int ldq, const nvc_bf16* 
   const int row_begin = cu_seqlens ? cu_seqlens[b] : b;
   const int qlen = cu_seqlens ? cu_seqlens[b + 1] - row_begin : 1;
   const int total = qlen * heads;
-  const int r0 = blockIdx.x * 16;
-  if (r0 >= total) return;
-  const int ctx_len = context_lens[b];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Two ways to spend the four warps.  Few rows (decode: one chunk of `heads` rows per sequence): the warps split the KEYS of
+  // one chunk and merge at the end.  Many rows (a prompt portion): every warp takes its OWN chunk and walks all of its
+  // keys alone - no merge, and the four neighbouring chunks read the same latent rows at about the same time.
+  const bool own = total >= 16 * kWarps;
+  const int chunk = own ? blockIdx.x * kWarps + warp : blockIdx.x;
+  const int r0 = chunk * 16;
+  if (r0 >= total) return;                 // CTA-uniform in the split mode (the only one with CTA barriers below)
+  const int tile_stride = own ? kTileTok : kCtaTok;
+  const int tile_first = own ? 0 : warp * kTileTok;
+  const int ctx_len = context_lens[b];
   const int quad = lane >> 2, tq = lane & 3;
   // rows of this thread's accumulator fragments
   const int ra = r0 + quad, rb = r0 + quad + 8;
@@ -60,7 +67,7 @@ latent_attn_mma_kernel(const nvc_bf16* __restrict__ q, int ldq, const nvc_bf16* 
   const int pa_ = va ? ctx_len - qlen + ta : -1, pb_ = vb ? ctx_len - qlen + tb : -1;   // last visible key
   const int last_row = min(r0 + 15, total - 1);
   const int kmax = ctx_len - qlen + last_row / heads;       // the farthest key any row of the chunk sees
-  const int n_tiles = (kmax + 1 + kCtaTok - 1) / kCtaTok;
+  const int n_tiles = (kmax + 1 + tile_stride - 1) / tile_stride;
   const int32_t* bt = block_tables + (int64_t)b * bt_stride;
 
   float o[NT][4];
@@ -71,7 +78,7 @@ latent_attn_mma_kernel(const nvc_bf16* __restrict__ q, int ldq, const nvc_bf16* 
 
   auto issue = [&](int i) {
     if (i < n_tiles) {
-      const int tok0 = i * kCtaTok + warp * kTileTok;
+      const int tok0 = i * tile_stride + tile_first;
       if (tok0 <= kmax) {
         const uint32_t st = ring + (i % kStages) * kStageBytes;
         // 32 lanes cover 16 rows x NC chunks in 16 * NC / 32 rounds
@@ -113,7 +120,7 @@ latent_attn_mma_kernel(const nvc_bf16* __restrict__ q, int ldq, const nvc_bf16* 
     issue(i + 2);
     cp_async_wait<2>();
     __syncwarp();
-    const int tok0 = i * kCtaTok + warp * kTileTok;
+    const int tok0 = i * tile_stride + tile_first;
     if (tok0 <= kmax) {                                // warp-uniform
       const uint32_t st = ring + (i % kStages) * kStageBytes;
       float s[2][4];
@@ -193,6 +200,19 @@ latent_attn_mma_kernel(const nvc_bf16* __restrict__ q, int ldq, const nvc_bf16* 
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
 
+  if (own) {
+    // ---- this warp's rows are complete: normalise and store the fragments (pairs of columns)
+    const float i0 = l0 > 0.f ? 1.0f / l0 : 0.f, i1 = l1 > 0.f ? 1.0f / l1 : 0.f;
+    nvc_bf16* o0 = out + (int64_t)(row_begin + ta) * ldo + (int64_t)ha * head_stride;
+    nvc_bf16* o1 = out + (int64_t)(row_begin + tb) * ldo + (int64_t)hb * head_stride;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int d = nt * 8 + 2 * tq;
+      if (va) *reinterpret_cast<uint32_t*>(o0 + d) = pack_bf16(o[nt][0] * i0, o[nt][1] * i0);
+      if (vb) *reinterpret_cast<uint32_t*>(o1 + d) = pack_bf16(o[nt][2] * i1, o[nt][3] * i1);
+    }
+    return;
+  }
   // ---- merge the warps (the rings are dead now)
   __syncthreads();
   float* sm_m = reinterpret_cast<float*>(smem);       // [kWarps][16]
