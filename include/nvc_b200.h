@@ -325,6 +325,10 @@ int nvc_linear_grouped(nvc_ctx* ctx, const void* A, int lda, const int32_t* a_ro
 int nvc_moe_route(nvc_ctx* ctx, const void* h, int h_dtype, int ldh, const float* w_router, const float* correction,
                   const float* w_shared_gate, int E, int top, float scale, int32_t* topk_idx, float* topk_w, float* gate, int N,
                   int H, void* stream);
+/* The same choice from router logits that a matrix product has already taken (z fp32 [N, ldz], the weights of the router
+ * as rows of one matrix); gate[n] = sigmoid(z[n, gate_col]) when gate_col >= 0. */
+int nvc_moe_route_logits(nvc_ctx* ctx, const float* z, int ldz, const float* correction, int E, int top, float scale, int gate_col,
+                         int32_t* topk_idx, float* topk_w, float* gate, int N, void* stream);
 /* Stable counting sort of the N * top (token, choice) pairs by expert: offsets [E + 1], src_rows [N * top] (token of the
  * pair at each sorted position), pos [N * top] (sorted position of pair n * top + t). */
 int nvc_moe_sort(nvc_ctx* ctx, const int32_t* topk_idx, int N, int top, int E, int32_t* offsets, int32_t* src_rows, int32_t* pos,

@@ -99,6 +99,7 @@ def _declare(l: C.CDLL) -> None:
         "nvc_linear": [_vp, _vp, _i, C.c_int64, _vp, _i, C.c_int64, _vp, _i, C.c_int64, _i, _i, _i, _i, _i, _i, _i, _vp],
         "nvc_linear_grouped": [_vp, _vp, _i, _vp, _vp, _i, C.c_int64, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
         "nvc_moe_route": [_vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _f, _vp, _vp, _vp, _i, _i, _vp],
+        "nvc_moe_route_logits": [_vp, _vp, _i, _vp, _i, _i, _f, _i, _vp, _vp, _vp, _i, _vp],
         "nvc_moe_sort": [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp],
         "nvc_moe_combine": [_vp, _vp, _i, _i, _vp, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _vp],
         "nvc_latent_attn_paged": [_vp, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _i, _i, _vp],

@@ -65,7 +65,9 @@ struct LayerW {
   // dense ff
   void *w_gu = nullptr, *w_fdown = nullptr;   // [2 ffp, Wp] (gate rows, then up rows at ffp), [Wp, ffp]
   // moe
-  float *router = nullptr, *corr = nullptr, *sg = nullptr;
+  void* router = nullptr;              // [Ep, Wp]: rows [0, E) = router, row E = the shared expert's gate vector
+  float* corr = nullptr;
+  int Ep = 0;
   void *w_eup = nullptr, *w_edown = nullptr;  // [E][effp, Wp], [E][Wp, effp]
   void *w_sup = nullptr, *w_sdown = nullptr;  // [sfp, Wp], [Wp, sfp]
   int qrp = 0, kvp = 0, dimp = 0, vdp = 0, ffp = 0, effp = 0, sfp = 0;
@@ -89,7 +91,7 @@ struct KaruzenBody : nvc_model_body {
   void *h = nullptr, *cq = nullptr, *q = nullptr, *qabs = nullptr, *olat = nullptr, *ao = nullptr, *gu = nullptr, *act = nullptr,
        *hid = nullptr, *su = nullptr, *hn = nullptr;
   int32_t *tk_idx = nullptr, *offsets = nullptr, *src_rows = nullptr, *pos = nullptr;
-  float *tk_w = nullptr, *gate = nullptr;
+  float *tk_w = nullptr, *gate = nullptr, *zlog = nullptr;
   float* tap_host = nullptr;
   size_t tap_cap = 0;
   bool prof_armed = false, prof_on = false;
@@ -172,7 +174,7 @@ struct KaruzenBody : nvc_model_body {
     const size_t slots = (size_t)r->opt.num_kvcache_blocks * r->opt.kvcache_block_size;
     int rc;
     L.resize(cfg.layers.size());
-    size_t m_down = 0, m_cq = 0, m_q = 0, m_qabs = 0, m_ao = 0, m_gu = 0, m_act = 0, m_hid = 0, m_su = 0, m_top = 0, m_E = 0;
+    size_t m_down = 0, m_cq = 0, m_q = 0, m_qabs = 0, m_ao = 0, m_gu = 0, m_act = 0, m_hid = 0, m_su = 0, m_top = 0, m_E = 0, m_Ep = 0;
     int64_t wbytes = 0;
     for (size_t i = 0; i < cfg.layers.size(); ++i) {
       const auto& m = cfg.layers[i].mixer;
@@ -208,7 +210,9 @@ struct KaruzenBody : nvc_model_body {
         m_act = std::max(m_act, (size_t)w.ffp);
       } else if (f.kind == nvc_karuzen_mlp::Moe) {
         w.effp = pad64(f.expert_ff);
-        if ((rc = zalloc(r, &w.router, (size_t)f.experts * cfg.width * 4)) || (rc = zalloc(r, &w.corr, f.experts * 4))) return rc;
+        w.Ep = pad64(f.experts + 1);
+        if ((rc = zalloc(r, &w.router, (size_t)w.Ep * Wp * esz)) || (rc = zalloc(r, &w.corr, f.experts * 4))) return rc;
+        m_Ep = std::max(m_Ep, (size_t)w.Ep);
         if ((rc = zalloc(r, &w.w_eup, (size_t)f.experts * w.effp * Wp * esz)) ||
             (rc = zalloc(r, &w.w_edown, (size_t)f.experts * Wp * w.effp * esz)))
           return rc;
@@ -221,9 +225,7 @@ struct KaruzenBody : nvc_model_body {
         }
         if (f.shared_ff > 0) {
           w.sfp = pad64(f.shared_ff);
-          if ((rc = zalloc(r, &w.w_sup, (size_t)w.sfp * Wp * esz)) || (rc = zalloc(r, &w.w_sdown, (size_t)Wp * w.sfp * esz)) ||
-              (rc = zalloc(r, &w.sg, cfg.width * 4)))
-            return rc;
+          if ((rc = zalloc(r, &w.w_sup, (size_t)w.sfp * Wp * esz)) || (rc = zalloc(r, &w.w_sdown, (size_t)Wp * w.sfp * esz))) return rc;
           wbytes += (int64_t)esz * 2 * f.shared_ff * cfg.width;
           for (const char* n : {"mlp.shared.up", "mlp.shared.down", "mlp.shared.sg"}) want[p + n] = false;
           m_su = std::max(m_su, (size_t)w.sfp);
@@ -249,7 +251,7 @@ struct KaruzenBody : nvc_model_body {
       return rc;
     if (m_gu && ((rc = zalloc(r, &gu, T * m_gu * esz)) || (rc = zalloc(r, &act, T * m_act * esz)))) return rc;
     if (m_top) {
-      if ((rc = zalloc(r, &tk_idx, T * m_top * 4)) || (rc = zalloc(r, &tk_w, T * m_top * 4)) || (rc = zalloc(r, &gate, T * 4)) ||
+      if ((rc = zalloc(r, &tk_idx, T * m_top * 4)) || (rc = zalloc(r, &tk_w, T * m_top * 4)) || (rc = zalloc(r, &gate, T * 4)) || (rc = zalloc(r, &zlog, T * m_Ep * 4)) ||
           (rc = zalloc(r, &offsets, (m_E + 1) * 4)) || (rc = zalloc(r, &src_rows, T * m_top * 4)) || (rc = zalloc(r, &pos, T * m_top * 4)) ||
           (rc = zalloc(r, &hid, T * m_hid * esz)) || (rc = zalloc(r, &y, T * m_top * Wp * 4)))
         return rc;
@@ -346,11 +348,11 @@ struct KaruzenBody : nvc_model_body {
         }
       }
       else if (sub == "mlp.down") { if (!shape_is(W, f.ff)) return bad(); rc = put_matrix(r, w.w_fdown, w.ffp, 0, 0, v.data(), W, f.ff, f.ff, 1); }
-      else if (sub == "mlp.router") { if (!shape_is(f.experts, W)) return bad(); rc = put_f32(r, w.router, v.data(), n); }
+      else if (sub == "mlp.router") { if (!shape_is(f.experts, W)) return bad(); rc = put_matrix(r, w.router, Wp, 0, 0, v.data(), f.experts, W, W, 1); }
       else if (sub == "mlp.correction") { if (n != (size_t)f.experts) return bad(); rc = put_f32(r, w.corr, v.data(), n); }
       else if (sub == "mlp.shared.up") { if (!shape_is(f.shared_ff, W)) return bad(); rc = put_matrix(r, w.w_sup, Wp, 0, 0, v.data(), f.shared_ff, W, W, 1); }
       else if (sub == "mlp.shared.down") { if (!shape_is(W, f.shared_ff)) return bad(); rc = put_matrix(r, w.w_sdown, w.sfp, 0, 0, v.data(), W, f.shared_ff, f.shared_ff, 1); }
-      else if (sub == "mlp.shared.sg") { if (n != (size_t)W) return bad(); rc = put_f32(r, w.sg, v.data(), W); }
+      else if (sub == "mlp.shared.sg") { if (n != (size_t)W) return bad(); rc = put_matrix(r, w.router, Wp, f.experts, 0, v.data(), 1, W, W, 1); }
       else if (sub.rfind("mlp.e", 0) == 0) {
         const size_t d2 = sub.find('.', 5);
         const int e = atoi(sub.substr(5, d2 - 5).c_str());
@@ -470,8 +472,10 @@ struct KaruzenBody : nvc_model_body {
         a1 = ffo;
       } else if (f.kind == nvc_karuzen_mlp::Moe) {
         const int P = N * f.top;
-        if ((rc = nvc_moe_route(ctx, h, dt, Wp, w.router, w.corr, w.sg, f.experts, f.top, f.router_scale, tk_idx, tk_w, w.sg ? gate : nullptr,
-                                N, W, st)))
+        // router logits (and the shared gate's, one more row) as one product with fp32 accumulation and output
+        if ((rc = nvc_linear(ctx, h, Wp, 0, w.router, Wp, 0, zlog, w.Ep, 0, dt, NVC_DT_F32, N, f.experts + 1, Wp, 1, NVC_ACT_NONE, st))) return rc;
+        if ((rc = nvc_moe_route_logits(ctx, zlog, w.Ep, w.corr, f.experts, f.top, f.router_scale, w.w_sup ? f.experts : -1, tk_idx, tk_w,
+                                       w.w_sup ? gate : nullptr, N, st)))
           return rc;
         mark(r, "moe_route");
         if ((rc = nvc_moe_sort(ctx, tk_idx, N, f.top, f.experts, offsets, src_rows, pos, st))) return rc;

@@ -10,39 +10,10 @@ namespace {
 // one warp per token.  Scores of up to 32 * kPerLane experts live in registers.
 constexpr int kMaxPerLane = 8;   // experts <= 256
 
-template <typename T>
-__global__ void moe_route_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ wr, const float* __restrict__ corr,
-                                 const float* __restrict__ wsg, int E, int top, float scale, int32_t* __restrict__ idx,
-                                 float* __restrict__ wout, float* __restrict__ gate, int N, int H) {
-  extern __shared__ float hs[];   // [warps][H]
-  pdl_trigger();
-  pdl_wait();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n = blockIdx.x * (blockDim.x >> 5) + warp;
-  if (n >= N) return;
-  float* x = hs + (size_t)warp * H;
-  for (int j = lane; j < H; j += 32) x[j] = ld_f(h + (int64_t)n * ldh + j);
-  __syncwarp();
-  float s[kMaxPerLane], c[kMaxPerLane];
-#pragma unroll
-  for (int i = 0; i < kMaxPerLane; ++i) {
-    const int e = lane + 32 * i;
-    s[i] = 0.f;
-    c[i] = -INFINITY;
-    if (e < E) {
-      float z = 0.f;
-      const float* w = wr + (int64_t)e * H;
-      for (int j = 0; j < H; ++j) z = fmaf(x[j], __ldg(w + j), z);
-      s[i] = sigmoid_f32(z);
-      c[i] = s[i] + __ldg(corr + e);
-    }
-  }
-  if (wsg && gate) {
-    float z = 0.f;
-    for (int j = lane; j < H; j += 32) z = fmaf(x[j], __ldg(wsg + j), z);
-    z = warp_sum(z);
-    if (lane == 0) gate[n] = sigmoid_f32(z);
-  }
+// top-k by repeated arg-max over the choice scores c (ties -> the lower expert index); expert e lives in lane e % 32,
+// slot e / 32.  Writes idx / weights of token n: s_chosen / (sum of the chosen s + 1e-20) * scale.
+__device__ __forceinline__ void topk_write(float (&s)[kMaxPerLane], float (&c)[kMaxPerLane], int lane, int E, int top, float scale,
+                                           int32_t* __restrict__ idx, float* __restrict__ wout, int64_t n) {
   // top-k by repeated arg-max over the choice scores (ties -> the lower expert index)
   float sel_sum = 0.f, my_w = 0.f;
   int my_e = 0;
@@ -79,41 +50,131 @@ __global__ void moe_route_kernel(const T* __restrict__ h, int ldh, const float* 
   for (int t = lane; t < top; t += 32) wout[(int64_t)n * top + t] *= inv;
 }
 
-// Counting sort by expert in one CTA (pairs = N * top).  Within an expert the pairs keep token order, so the
-// layout - and with it every sum downstream - does not depend on thread timing.
-__global__ void moe_sort_kernel(const int32_t* __restrict__ idx, int P, int top, int E, int32_t* __restrict__ offsets,
-                                int32_t* __restrict__ src_rows, int32_t* __restrict__ pos) {
-  extern __shared__ int32_t sm[];   // [E] counts, then [E + 1] offsets
-  int32_t* cnt = sm;
-  int32_t* off = sm + E;
+// scores from logits that a matrix product has already taken: z [N, ldz] fp32, column gate_col (if >= 0) = the shared gate
+__global__ void moe_topk_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ corr, int E, int top, float scale,
+                                int gate_col, int32_t* __restrict__ idx, float* __restrict__ wout, float* __restrict__ gate, int N) {
   pdl_trigger();
   pdl_wait();
-  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (n >= N) return;
+  const float* zr = z + (int64_t)n * ldz;
+  float s[kMaxPerLane], c[kMaxPerLane];
+#pragma unroll
+  for (int i = 0; i < kMaxPerLane; ++i) {
+    const int e = lane + 32 * i;
+    s[i] = 0.f;
+    c[i] = -INFINITY;
+    if (e < E) {
+      s[i] = sigmoid_f32(zr[e]);
+      c[i] = s[i] + __ldg(corr + e);
+    }
+  }
+  if (gate_col >= 0 && gate && lane == 0) gate[n] = sigmoid_f32(zr[gate_col]);
+  topk_write(s, c, lane, E, top, scale, idx, wout, n);
+}
+
+template <typename T>
+__global__ void moe_route_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ wr, const float* __restrict__ corr,
+                                 const float* __restrict__ wsg, int E, int top, float scale, int32_t* __restrict__ idx,
+                                 float* __restrict__ wout, float* __restrict__ gate, int N, int H) {
+  extern __shared__ float hs[];   // [warps][H]
+  pdl_trigger();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (n >= N) return;
+  float* x = hs + (size_t)warp * H;
+  for (int j = lane; j < H; j += 32) x[j] = ld_f(h + (int64_t)n * ldh + j);
+  __syncwarp();
+  // expert e's score lives in lane e % 32, slot e / 32; every dot product is taken by the whole warp (coalesced weight rows)
+  float s[kMaxPerLane], c[kMaxPerLane];
+#pragma unroll
+  for (int i = 0; i < kMaxPerLane; ++i) { s[i] = 0.f; c[i] = -INFINITY; }
+  for (int e0 = 0; e0 < E; e0 += 4) {           // four experts at a time: independent loads and sums
+    float z[4] = {0.f, 0.f, 0.f, 0.f};
+    const float* w0 = wr + (int64_t)e0 * H;
+#pragma unroll 4
+    for (int j = lane; j < H; j += 32) {
+      const float xv = x[j];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (e0 + u < E) z[u] = fmaf(xv, __ldg(w0 + (int64_t)u * H + j), z[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int e = e0 + u;
+      const float zu = warp_sum(z[u]);
+      if (e < E && lane == (e & 31)) {
+        const float sv = sigmoid_f32(zu), cv = sv + __ldg(corr + e);
+#pragma unroll
+        for (int i = 0; i < kMaxPerLane; ++i)
+          if (i == (e >> 5)) { s[i] = sv; c[i] = cv; }
+      }
+    }
+  }
+  if (wsg && gate) {
+    float z = 0.f;
+    for (int j = lane; j < H; j += 32) z = fmaf(x[j], __ldg(wsg + j), z);
+    z = warp_sum(z);
+    if (lane == 0) gate[n] = sigmoid_f32(z);
+  }
+  topk_write(s, c, lane, E, top, scale, idx, wout, n);
+}
+
+// Stable counting sort by expert in one CTA of 32 warps (pairs = N * top).  Warp w owns the contiguous segment w of the
+// pairs: it counts its pairs per expert, a prefix over (expert, warp) gives every warp its first position in every
+// expert's group, and the warp then places its pairs in order (__match_any_sync ranks equal experts inside a batch of
+// 32).  Within an expert the pairs keep token order, so the layout - and every sum downstream - is deterministic.
+__global__ void __launch_bounds__(1024)
+moe_sort_kernel(const int32_t* __restrict__ idx, int P, int top, int E, int32_t* __restrict__ offsets,
+                int32_t* __restrict__ src_rows, int32_t* __restrict__ pos) {
+  extern __shared__ int32_t sm[];   // [32][E] counts -> starts, then [E + 1] offsets
+  int32_t* cnt = sm;
+  int32_t* off = sm + 32 * E;
+  pdl_trigger();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < 32 * E; i += blockDim.x) cnt[i] = 0;
   __syncthreads();
-  for (int p = threadIdx.x; p < P; p += blockDim.x) atomicAdd(&cnt[idx[p]], 1);
+  const int seg = ((P + 31) / 32 + 31) / 32 * 32;      // pairs per warp, a multiple of 32
+  const int p_begin = warp * seg, p_end = min(P, p_begin + seg);
+  for (int p = p_begin + lane; p < p_end; p += 32) atomicAdd(&cnt[warp * E + idx[p]], 1);
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int a = 0;
-    for (int e = 0; e < E; ++e) { off[e] = a; a += cnt[e]; }
-    off[E] = a;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int total = 0;
+    for (int w = 0; w < 32; ++w) total += cnt[w * E + e];
+    off[e + 1] = total;                                  // sizes for now
   }
   __syncthreads();
-  for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = off[e];
-  // expert e is filled by one warp at a time walking the pairs in order: stable
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-  for (int e = warp; e < E; e += warps) {
-    int fill = off[e];
-    for (int p0 = 0; p0 < P; p0 += 32) {
-      const int p = p0 + lane;
-      const bool mine = p < P && idx[p] == e;
-      const unsigned m = __ballot_sync(0xffffffffu, mine);
-      if (mine) {
-        const int at = fill + __popc(m & ((1u << lane) - 1));
-        src_rows[at] = p / top;
-        pos[p] = at;
-      }
-      fill += __popc(m);
+  if (threadIdx.x == 0) {
+    off[0] = 0;
+    for (int e = 0; e < E; ++e) off[e + 1] += off[e];
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {    // counts -> first position of (warp, expert)
+    int a = off[e];
+    for (int w = 0; w < 32; ++w) {
+      const int n = cnt[w * E + e];
+      cnt[w * E + e] = a;
+      a += n;
     }
+  }
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = off[e];
+  __syncthreads();
+  for (int p0 = p_begin; p0 < p_end; p0 += 32) {
+    const int p = p0 + lane;
+    const bool have = p < p_end;
+    const int e = have ? idx[p] : -1 - lane;             // absent lanes match nobody
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    if (have) {
+      const int at = cnt[warp * E + e] + __popc(peers & ((1u << lane) - 1));
+      src_rows[at] = p / top;
+      pos[p] = at;
+    }
+    __syncwarp();
+    if (have && lane == 31 - __clz(peers)) cnt[warp * E + e] += __popc(peers);   // the last peer advances the group
+    __syncwarp();
   }
 }
 
@@ -154,11 +215,23 @@ int nvc_moe_route(nvc_ctx* ctx, const void* h, int h_dtype, int ldh, const float
   return NVC_OK;
 }
 
+int nvc_moe_route_logits(nvc_ctx* ctx, const float* z, int ldz, const float* correction, int E, int top, float scale, int gate_col,
+                         int32_t* topk_idx, float* topk_w, float* gate, int N, void* stream) {
+  NVC_REQUIRE(ctx, ctx && z && correction && topk_idx && topk_w, NVC_EINVAL, "null pointer");
+  NVC_REQUIRE(ctx, E > 0 && E <= 32 * kMaxPerLane && top > 0 && top <= E, NVC_ESHAPE, "experts must be in [1, 256], top in [1, experts]");
+  NVC_REQUIRE(ctx, N >= 0 && ldz >= E && gate_col < ldz && (gate_col < 0 || gate), NVC_EINVAL, "bad sizes");
+  if (N == 0) return NVC_OK;
+  NVC_CUDA_CHECK(ctx, nvc_launch(ctx, moe_topk_kernel, dim3((N + 3) / 4), dim3(128), 0, nvc_stream(stream), z, ldz, correction, E, top, scale,
+                                 gate_col, topk_idx, topk_w, gate, N));
+  ctx->launches++;
+  return NVC_OK;
+}
+
 int nvc_moe_sort(nvc_ctx* ctx, const int32_t* topk_idx, int N, int top, int E, int32_t* offsets, int32_t* src_rows, int32_t* pos,
                  void* stream) {
   NVC_REQUIRE(ctx, ctx && topk_idx && offsets && src_rows && pos, NVC_EINVAL, "null pointer");
-  NVC_REQUIRE(ctx, N >= 0 && top > 0 && E > 0 && E <= 4096, NVC_EINVAL, "bad sizes");
-  NVC_CUDA_CHECK(ctx, nvc_launch(ctx, moe_sort_kernel, dim3(1), dim3(1024), (size_t)(2 * E + 1) * sizeof(int32_t), nvc_stream(stream),
+  NVC_REQUIRE(ctx, N >= 0 && top > 0 && E > 0 && E <= 320, NVC_EINVAL, "bad sizes");
+  NVC_CUDA_CHECK(ctx, nvc_launch(ctx, moe_sort_kernel, dim3(1), dim3(1024), (size_t)(33 * E + 1) * sizeof(int32_t), nvc_stream(stream),
                                  topk_idx, N * top, top, E, offsets, src_rows, pos));
   ctx->launches++;
   return NVC_OK;

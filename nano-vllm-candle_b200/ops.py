@@ -394,6 +394,17 @@ def moe_route(ctx, h, w_router, correction, w_gate, top: int, scale: float):
     return idx, w, gate
 
 
+def moe_route_logits(ctx, z: torch.Tensor, correction, E: int, top: int, scale: float, gate_col: int = -1):
+    """z: fp32 [N, >= E] router logits (column gate_col: the shared gate's logit)."""
+    N = z.shape[0]
+    idx = torch.empty(N, top, dtype=torch.int32, device=z.device)
+    w = torch.empty(N, top, dtype=torch.float32, device=z.device)
+    gate = torch.empty(N, dtype=torch.float32, device=z.device) if gate_col >= 0 else None
+    check(ctx.l.nvc_moe_route_logits(ctx.h, _ptr(z), z.stride(0), _ptr(correction), E, top, scale, gate_col, _ptr(idx), _ptr(w), _ptr(gate),
+                                     N, _stream()), "nvc_moe_route_logits", ctx.h)
+    return idx, w, gate
+
+
 def moe_sort(ctx, idx: torch.Tensor, E: int):
     N, top = idx.shape
     offsets = torch.empty(E + 1, dtype=torch.int32, device=idx.device)

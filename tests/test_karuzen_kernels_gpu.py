@@ -145,6 +145,12 @@ def test_moe_route_sort_combine(ctx, ops, E, top):
     dense = torch.zeros(N, E).scatter(1, idx.cpu().long(), w.cpu())
     assert torch.allclose(dense, torch.zeros(N, E).scatter(1, widx, ww), rtol=1e-5, atol=1e-6)
     assert torch.allclose(gate.cpu(), torch.sigmoid(h @ sg), rtol=1e-5, atol=1e-6)
+    # the same choice from logits taken by a matrix product (one more column: the shared gate)
+    z = torch.cat([h @ router.T, (h @ sg).unsqueeze(1), torch.full((N, 3), float("nan"))], 1)
+    idx2, w2, gate2 = ops.moe_route_logits(ctx, z.to(DEV), corr.to(DEV), E, top, 2.5, gate_col=E)
+    assert torch.equal(idx2.cpu().long().sort(-1).values, widx.sort(-1).values)
+    assert torch.allclose(torch.zeros(N, E).scatter(1, idx2.cpu().long(), w2.cpu()), torch.zeros(N, E).scatter(1, widx, ww), rtol=1e-5, atol=1e-6)
+    assert torch.allclose(gate2.cpu(), torch.sigmoid(h @ sg), rtol=1e-5, atol=1e-6)
     offsets, src, pos = ops.moe_sort(ctx, idx, E)
     o, s, p = offsets.cpu().tolist(), src.cpu().tolist(), pos.cpu().tolist()
     assert o[0] == 0 and o[-1] == N * top
@@ -153,6 +159,8 @@ def test_moe_route_sort_combine(ctx, ops, E, top):
         assert o[e + 1] - o[e] == flat.count(e)
     for pair, at in enumerate(p):
         assert o[flat[pair]] <= at < o[flat[pair] + 1] and s[at] == pair // top
+    for e in range(E):          # stable: inside an expert's group the tokens ascend
+        assert s[o[e]:o[e + 1]] == sorted(s[o[e]:o[e + 1]])
     assert sorted(p) == list(range(N * top))
     y = torch.randn(N * top, H, generator=g)
     shared = torch.randn(N, H, generator=g)
