@@ -170,8 +170,11 @@ def make_weights(cfg: dict, seed: int = 0, bf16_values: bool = True) -> Dict[str
         t = torch.randn(*shape, generator=g) * s
         return t.bfloat16().float() if bf16_values else t
 
+    def fix(t):
+        return t.bfloat16().float() if bf16_values else t
+
     def norm(prefix):
-        return {prefix: 1.0 + rnd(W, s=0.2), prefix + ".b": rnd(W, s=0.1), prefix + ".alpha": (0.5 + 0.3 * torch.rand((), generator=g)).bfloat16().float()}
+        return {prefix: fix(1.0 + rnd(W, s=0.2)), prefix + ".b": rnd(W, s=0.1), prefix + ".alpha": fix(0.5 + 0.3 * torch.rand((), generator=g))}
 
     w = {"embed": rnd(cfg["vocab"], W, s=1.0)}
     w.update(norm("final.norm"))
@@ -180,10 +183,10 @@ def make_weights(cfg: dict, seed: int = 0, bf16_values: bool = True) -> Dict[str
         w.update(norm(p + "norm1"))
         H, d, vd, kr, qr = m["heads"], m["dim"], m["vdim"], m["kv_rank"], m["q_rank"]
         w[p + "mix.dq"] = rnd(qr, W, s=W ** -0.5)
-        w[p + "mix.dq.norm"] = 1.0 + rnd(qr, s=0.2)
+        w[p + "mix.dq.norm"] = fix(1.0 + rnd(qr, s=0.2))
         w[p + "mix.uq"] = rnd(H * d, qr, s=qr ** -0.5)
         w[p + "mix.dkv"] = rnd(kr, W, s=W ** -0.5)
-        w[p + "mix.dkv.norm"] = 1.0 + rnd(kr, s=0.2)
+        w[p + "mix.dkv.norm"] = fix(1.0 + rnd(kr, s=0.2))
         w[p + "mix.uk"] = rnd(H * d, kr, s=kr ** -0.5)
         w[p + "mix.uv"] = rnd(H * vd, kr, s=kr ** -0.5)
         w[p + "mix.o"] = rnd(W, H * vd, s=(H * vd) ** -0.5)

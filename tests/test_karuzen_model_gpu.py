@@ -211,3 +211,59 @@ def test_greedy_generation_through_the_scheduler(dtype, chunked):
         assert r.engine.num_free_blocks() == 24
     finally:
         r.close()
+
+
+def write_model_dir(path, cfg, weights):
+    """config.json + model.safetensors (bf16) the way a checkpoint of this design is stored."""
+    import json
+    import struct
+    header, blobs, at = {}, [], 0
+    for name, t in weights.items():
+        raw = t.bfloat16().contiguous().view(torch.int16).numpy().tobytes()
+        header[name] = {"dtype": "BF16", "shape": list(t.shape), "data_offsets": [at, at + len(raw)]}
+        blobs.append(raw)
+        at += len(raw)
+    hj = json.dumps(header).encode()
+    hj += b" " * (-len(hj) % 8)
+    with open(path / "model.safetensors", "wb") as f:
+        f.write(struct.pack("<Q", len(hj)) + hj + b"".join(blobs))
+    (path / "config.json").write_text(json.dumps(cfg))
+
+
+def test_command_line_tools_on_a_checkpoint_directory(tmp_path):
+    """bin/trace_run and bin/generate: registry by config.json, native safetensors loader, the engine underneath."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = cfg_a()
+    w = K.make_weights(cfg, 9)
+    oracle = K.KaruzenOracle(cfg, w)
+    write_model_dir(tmp_path, cfg, w)
+    V = cfg["vocab"]
+    pa, pb = toks(41, V, 1), toks(9, V, 2)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": pa[:30], "want": [0, 29]}, {"id": "b", "tokens": pb[:2], "want": []}], "end": []},
+             {"step": 1, "entries": [{"id": "b", "tokens": pb[2:], "want": [6]}, {"id": "a", "tokens": pa[30:31], "want": [0]}], "end": ["b"]},
+             {"step": 2, "entries": [{"id": "a", "tokens": pa[31:], "want": [9]}, {"id": "b", "tokens": pb, "want": [8]}], "end": ["a", "b"]}]
+    out = tmp_path / "out"
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", str(tmp_path), "--dtype", "float32", "--out", str(out),
+                        "--max-tokens", "128"], input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [ln for ln in r.stdout.splitlines() if ln.startswith("done")] == ["done 0", "done 1", "done 2"]
+    la, lb = oracle.forward(pa).numpy(), oracle.forward(pb).numpy()
+    want = {0: np.stack([la[0], la[29]]), 1: np.stack([lb[8], la[30]]), 2: np.stack([la[40], lb[8]])}
+    for n, wv in want.items():
+        got = np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(-1, V)
+        assert got.shape == wv.shape and Rig.rel_err(got, wv).max() < 1e-4, f"step {n}"
+    g = subprocess.run([sys.executable, os.path.join(root, "bin", "generate"), "--model", str(tmp_path), "--dtype", "float32", "--prompt-ids",
+                        ",".join(map(str, pb)) + ";" + ",".join(map(str, pa[:5])), "--max-tokens", "6", "--block-size", "16"],
+                       capture_output=True, text=True, timeout=600)
+    assert g.returncode == 0, g.stderr[-2000:]
+    lines = [json.loads(ln) for ln in g.stdout.splitlines() if ln.startswith("{")]
+    assert [ln["prompt"] for ln in lines] == [pb, pa[:5]]
+    for ln in lines:
+        lg = oracle.forward(ln["prompt"] + ln["tokens"][:-1]).numpy()
+        for i, t in enumerate(ln["tokens"]):
+            row = lg[len(ln["prompt"]) - 1 + i]
+            assert row.max() - row[t] <= 1e-3
