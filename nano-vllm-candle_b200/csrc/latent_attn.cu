@@ -125,7 +125,7 @@ extern "C" int nvc_latent_attn_paged(nvc_ctx* ctx, const void* q, int ldq, const
   static const bool mma_env = !(getenv("NVC_LATENT_ATTN_MMA") && atoi(getenv("NVC_LATENT_ATTN_MMA")) == 0);
   if (dtype == NVC_DT_BF16 && mma_env && (head_stride == 64 || head_stride == 128) && ldc >= head_stride && ldc % 8 == 0 &&
       ldq % 2 == 0 && ldo % 2 == 0 && ((uintptr_t)cache % 16) == 0 && ((uintptr_t)q % 4) == 0 && ((uintptr_t)out % 4) == 0) {
-    // padding columns [D, head_stride) of q and of the cache rows are zero by contract
+    // padding columns [D, head_stride) of q and of the cache rows are zero (the caller guarantees it)
     const dim3 grid(((size_t)max_qlen * heads + 15) / 16, B);
     const float sl2 = scale * 1.4426950408889634f;
     if (head_stride == 64) {

@@ -211,7 +211,7 @@ def attn_want(q, c, scale):
 
 
 @pytest.mark.parametrize("dt", DTS)
-@pytest.mark.parametrize("heads,D,bs", [(3, 40, 16), (6, 64, 64), (1, 8, 32), (5, 96, 16), (16, 128, 64)])
+@pytest.mark.parametrize("heads,D,bs", [(3, 40, 16), (7, 64, 64), (1, 8, 32), (5, 96, 16), (16, 128, 64)])
 def test_latent_attention_mixed_batch(ctx, ops, dt, heads, D, bs):
     """Portions behind cached prefixes, whole prompts and single decode rows in one launch, unwritten slots poisoned."""
     g = torch.Generator().manual_seed(11)
