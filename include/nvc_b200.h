@@ -342,10 +342,13 @@ int nvc_moe_combine(nvc_ctx* ctx, const void* y, int y_dtype, int ldy, const int
  * q / out: [rows, heads, head_stride] with row strides ldq / ldo; sequence b owns rows cu_seqlens[b] .. cu_seqlens[b + 1]
  * (cu_seqlens == NULL: one row per sequence), which are the LAST positions of its context_lens[b] tokens; the slot of token
  * j is block_tables[b, j / block_size] * block_size + j % block_size.  D <= 512.  bf16 rows with head_stride 64 or 128 run
- * on the tensor pipe and read head_stride numbers per row: columns [D, head_stride) of q and of the cache rows must be zero. */
+ * on the tensor pipe and read head_stride numbers per row: columns [D, head_stride) of q and of the cache rows must be zero.
+ * workspace (optional, device memory): lets a decode launch (max_qlen == 1) of a small batch split every sequence's keys
+ * over up to 8 CTAs; B * ceil(heads / 16) * 16 * splits * (2 + head_stride) floats are used, fewer splits if it is smaller. */
 int nvc_latent_attn_paged(nvc_ctx* ctx, const void* q, int ldq, const void* cache, int ldc, const int32_t* block_tables,
                           int bt_stride, const int32_t* context_lens, const int32_t* cu_seqlens, int B, int max_qlen, int heads,
-                          int D, int head_stride, int block_size, float scale, void* out, int ldo, int dtype, void* stream);
+                          int D, int head_stride, int block_size, float scale, void* out, int ldo, int dtype, void* workspace,
+                          size_t workspace_bytes, void* stream);
 
 /* K8. Replaces Qwen3ModelRunner::argmax (src/engine/llm_engine.rs:135-142) on device:
  * idx[b] = LAST index of the maximum of logits[b, :] (Iterator::max_by tie rule);

@@ -102,7 +102,7 @@ def _declare(l: C.CDLL) -> None:
         "nvc_moe_route_logits": [_vp, _vp, _i, _vp, _i, _i, _f, _i, _vp, _vp, _vp, _i, _vp],
         "nvc_moe_sort": [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp],
         "nvc_moe_combine": [_vp, _vp, _i, _i, _vp, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _vp],
-        "nvc_latent_attn_paged": [_vp, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _i, _i, _vp],
+        "nvc_latent_attn_paged": [_vp, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _i, _i, _vp, _sz, _vp],
         "nvc_debug_set": [_i, _i],
     }
     for name, args in sigs.items():

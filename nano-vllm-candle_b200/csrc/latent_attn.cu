@@ -8,6 +8,7 @@
 //
 // nvc_latent_attn_paged: the tensor-pipe kernel (latent_attn_mma.cuh) for bf16 rows of 64 or 128 numbers, else the fp32 FMA
 // kernel below (the exact mode, and any other width).
+#include <algorithm>
 #include <cstdlib>
 
 #include "typed.cuh"
@@ -116,7 +117,7 @@ latent_attn_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache
 extern "C" int nvc_latent_attn_paged(nvc_ctx* ctx, const void* q, int ldq, const void* cache, int ldc, const int32_t* block_tables,
                                      int bt_stride, const int32_t* context_lens, const int32_t* cu_seqlens, int B, int max_qlen,
                                      int heads, int D, int head_stride, int block_size, float scale, void* out, int ldo, int dtype,
-                                     void* stream) {
+                                     void* workspace, size_t workspace_bytes, void* stream) {
   NVC_REQUIRE(ctx, ctx && q && cache && block_tables && context_lens && out, NVC_EINVAL, "null pointer");
   NVC_REQUIRE(ctx, B >= 0 && max_qlen > 0 && heads > 0 && D > 0 && block_size > 0 && bt_stride > 0, NVC_EINVAL, "bad sizes");
   NVC_REQUIRE(ctx, D <= 32 * kMaxDPerLane, NVC_ESHAPE, "latent size above 512");
@@ -126,19 +127,35 @@ extern "C" int nvc_latent_attn_paged(nvc_ctx* ctx, const void* q, int ldq, const
   if (dtype == NVC_DT_BF16 && mma_env && (head_stride == 64 || head_stride == 128) && ldc >= head_stride && ldc % 8 == 0 &&
       ldq % 2 == 0 && ldo % 2 == 0 && ((uintptr_t)cache % 16) == 0 && ((uintptr_t)q % 4) == 0 && ((uintptr_t)out % 4) == 0) {
     // padding columns [D, head_stride) of q and of the cache rows are zero (the caller guarantees it)
-    const dim3 grid(((size_t)max_qlen * heads + 15) / 16, B);
+    const int chunks = (int)(((size_t)max_qlen * heads + 15) / 16);
+    // a decode launch that would leave most SMs idle splits every sequence's keys over several CTAs (partials in the
+    // caller's workspace, merged by a second kernel)
+    int S = 1;
+    if (max_qlen == 1 && workspace && heads < 16 * latmma::kWarps) {     // (more heads: every warp owns a chunk, no split)
+      S = std::min(8, std::max(1, (2 * ctx->num_sms) / (chunks * B)));
+      while (S > 1 && (size_t)B * chunks * 16 * S * (2 + head_stride) * sizeof(float) > workspace_bytes) --S;
+    }
+    const dim3 grid(chunks, B, S);
     const float sl2 = scale * 1.4426950408889634f;
+    float* part = reinterpret_cast<float*>(workspace);
     if (head_stride == 64) {
       NVC_CUDA_CHECK(ctx, nvc_launch(ctx, latmma::latent_attn_mma_kernel<64>, grid, dim3(latmma::kWarps * 32), latmma::smem_bytes<64>(),
                                      nvc_stream(stream), reinterpret_cast<const nvc_bf16*>(q), ldq, reinterpret_cast<const nvc_bf16*>(cache),
                                      ldc, block_tables, bt_stride, context_lens, cu_seqlens, heads, head_stride, block_size, sl2,
-                                     reinterpret_cast<nvc_bf16*>(out), ldo));
+                                     reinterpret_cast<nvc_bf16*>(out), ldo, part, S));
+      if (S > 1)
+        NVC_CUDA_CHECK(ctx, nvc_launch(ctx, latmma::latent_attn_combine_kernel<64>, dim3(B * chunks * 16), dim3(64), 0, nvc_stream(stream),
+                                       (const float*)part, S, chunks, cu_seqlens, heads, head_stride, reinterpret_cast<nvc_bf16*>(out), ldo));
     } else {
       NVC_CUDA_CHECK(ctx, nvc_launch(ctx, latmma::latent_attn_mma_kernel<128>, grid, dim3(latmma::kWarps * 32), latmma::smem_bytes<128>(),
                                      nvc_stream(stream), reinterpret_cast<const nvc_bf16*>(q), ldq, reinterpret_cast<const nvc_bf16*>(cache),
                                      ldc, block_tables, bt_stride, context_lens, cu_seqlens, heads, head_stride, block_size, sl2,
-                                     reinterpret_cast<nvc_bf16*>(out), ldo));
+                                     reinterpret_cast<nvc_bf16*>(out), ldo, part, S));
+      if (S > 1)
+        NVC_CUDA_CHECK(ctx, nvc_launch(ctx, latmma::latent_attn_combine_kernel<128>, dim3(B * chunks * 16), dim3(128), 0, nvc_stream(stream),
+                                       (const float*)part, S, chunks, cu_seqlens, heads, head_stride, reinterpret_cast<nvc_bf16*>(out), ldo));
     }
+    if (S > 1) ctx->launches++;
     ctx->launches++;
     return NVC_OK;
   }

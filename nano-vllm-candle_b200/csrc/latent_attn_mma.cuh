@@ -33,7 +33,7 @@ __global__ void __launch_bounds__(kWarps * 32)
 latent_attn_mma_kernel(const nvc_bf16* __restrict__ q, int ldq, const nvc_bf16* __restrict__ cache, int ldc,
                        const int32_t* __restrict__ block_tables, int bt_stride, const int32_t* __restrict__ context_lens,
                        const int32_t* __restrict__ cu_seqlens, int heads, int head_stride, int block_size, float scale_log2e,
-                       nvc_bf16* __restrict__ out, int ldo) {
+                       nvc_bf16* __restrict__ out, int ldo, float* __restrict__ part, int num_splits) {
   constexpr int RB = DP * 2;               // bytes per latent row
   constexpr int NC = DP / 8;               // 16-byte chunks per row
   constexpr int KS = DP / 16;              // k-steps of S
@@ -55,8 +55,10 @@ latent_attn_mma_kernel(const nvc_bf16* __restrict__ q, int ldq, const nvc_bf16* 
   const int chunk = own ? blockIdx.x * kWarps + warp : blockIdx.x;
   const int r0 = chunk * 16;
   if (r0 >= total) return;                 // CTA-uniform in the split mode (the only one with CTA barriers below)
-  const int tile_stride = own ? kTileTok : kCtaTok;
-  const int tile_first = own ? 0 : warp * kTileTok;
+  // key split over CTAs (decode launches of small batches): CTA z takes the 64-token tiles z, z + S, z + 2S, ...
+  const int S = own ? 1 : num_splits, split = own ? 0 : blockIdx.z;
+  const int tile_stride = own ? kTileTok : kCtaTok * S;
+  const int tile_first = own ? 0 : split * kCtaTok + warp * kTileTok;
   const int ctx_len = context_lens[b];
   const int quad = lane >> 2, tq = lane & 3;
   // rows of this thread's accumulator fragments
@@ -67,7 +69,8 @@ latent_attn_mma_kernel(const nvc_bf16* __restrict__ q, int ldq, const nvc_bf16* 
   const int pa_ = va ? ctx_len - qlen + ta : -1, pb_ = vb ? ctx_len - qlen + tb : -1;   // last visible key
   const int last_row = min(r0 + 15, total - 1);
   const int kmax = ctx_len - qlen + last_row / heads;       // the farthest key any row of the chunk sees
-  const int n_tiles = (kmax + 1 + tile_stride - 1) / tile_stride;
+  const int n_tiles = own ? (kmax + 1 + kTileTok - 1) / kTileTok
+                          : ((kmax + 1 + kCtaTok - 1) / kCtaTok - split + S - 1) / S;   // 64-token tiles of this split (may be <= 0)
   const int32_t* bt = block_tables + (int64_t)b * bt_stride;
 
   float o[NT][4];
@@ -247,7 +250,41 @@ latent_attn_mma_kernel(const nvc_bf16* __restrict__ q, int ldq, const nvc_bf16* 
       L += sm_l[w * 16 + g] * wt;
       O += sm_o[(w * 16 + g) * DP + d] * wt;
     }
-    const int rr = r0 + g, t = rr / heads, h = rr - t * heads;
+    if (S == 1) {
+      const int rr = r0 + g, t = rr / heads, h = rr - t * heads;
+      out[(int64_t)(row_begin + t) * ldo + (int64_t)h * head_stride + d] = __bfloat16_as_ushort(__float2bfloat16_rn(L > 0.f ? O / L : 0.f));
+    } else {
+      // partial (max, sum, un-normalised row) of this split: [b][chunk][row][split][2 + DP]
+      float* p = part + ((((int64_t)b * gridDim.x + chunk) * 16 + g) * S + split) * (2 + DP);
+      if (d == 0) { __stcg(p, M); __stcg(p + 1, L); }
+      __stcg(p + 2 + d, O);
+    }
+  }
+}
+
+// merges the splits of every row: out = sum_s O_s 2^(M_s - M) / sum_s L_s 2^(M_s - M)
+template <int DP>
+__global__ void latent_attn_combine_kernel(const float* __restrict__ part, int S, int chunks, const int32_t* __restrict__ cu_seqlens,
+                                           int heads, int head_stride, nvc_bf16* __restrict__ out, int ldo) {
+  pdl_trigger();
+  pdl_wait();
+  const int g = blockIdx.x & 15, chunk = (blockIdx.x >> 4) % chunks, b = (blockIdx.x >> 4) / chunks;
+  const int row_begin = cu_seqlens ? cu_seqlens[b] : b;
+  const int qlen = cu_seqlens ? cu_seqlens[b + 1] - row_begin : 1;
+  const int rr = chunk * 16 + g;
+  if (rr >= qlen * heads) return;
+  const float* p = part + (((int64_t)b * chunks + chunk) * 16 + g) * S * (2 + DP);
+  float M = -INFINITY;
+  for (int s = 0; s < S; ++s) M = fmaxf(M, p[s * (2 + DP)]);
+  const int t = rr / heads, h = rr - t * heads;
+  for (int d = threadIdx.x; d < DP; d += blockDim.x) {
+    float L = 0.f, O = 0.f;
+    for (int s = 0; s < S; ++s) {
+      const float ms = p[s * (2 + DP)];
+      const float wt = ms == -INFINITY ? 0.f : fast_exp2(ms - M);
+      L += p[s * (2 + DP) + 1] * wt;
+      O += p[s * (2 + DP) + 2 + d] * wt;
+    }
     out[(int64_t)(row_begin + t) * ldo + (int64_t)h * head_stride + d] = __bfloat16_as_ushort(__float2bfloat16_rn(L > 0.f ? O / L : 0.f));
   }
 }

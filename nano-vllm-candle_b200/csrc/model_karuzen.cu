@@ -92,6 +92,8 @@ struct KaruzenBody : nvc_model_body {
        *hid = nullptr, *su = nullptr, *hn = nullptr;
   int32_t *tk_idx = nullptr, *offsets = nullptr, *src_rows = nullptr, *pos = nullptr;
   float *tk_w = nullptr, *gate = nullptr, *zlog = nullptr;
+  void* attn_ws = nullptr;             // key-split partials of small decode batches
+  size_t attn_ws_bytes = 0;
   float* tap_host = nullptr;
   size_t tap_cap = 0;
   bool prof_armed = false, prof_on = false;
@@ -258,6 +260,12 @@ struct KaruzenBody : nvc_model_body {
       if (m_su && ((rc = zalloc(r, &su, T * m_su * esz)) || (rc = zalloc(r, &sd, T * Wp * 4)))) return rc;
     }
     if ((rc = zalloc(r, &hn, (size_t)r->max_logit_rows * Wp * esz))) return rc;
+    {
+      size_t chunks = 1;
+      for (auto& ly : cfg.layers) chunks = std::max(chunks, (size_t)(ly.mixer.heads + 15) / 16);
+      attn_ws_bytes = std::min<size_t>((size_t)r->opt.max_num_seqs, (size_t)2 * ctx->num_sms) * chunks * 16 * 8 * (2 + 128) * sizeof(float);
+      if ((rc = zalloc(r, &attn_ws, attn_ws_bytes))) return rc;
+    }
     return NVC_OK;
   }
 
@@ -443,7 +451,7 @@ struct KaruzenBody : nvc_model_body {
       mark(r, "absorb_uk");
       if ((rc = nvc_latent_attn_paged(ctx, qabs, lw, cache[k], w.kvp, r->d_bt, r->max_blocks_cap, r->d_ctx, s.decode ? nullptr : r->d_cu,
                                       s.B, s.decode ? 1 : s.max_seqlen, m.heads, m.kv_rank, w.kvp, r->opt.kvcache_block_size, m.scale,
-                                      olat, lw, dt, st)))
+                                      olat, lw, dt, attn_ws, attn_ws_bytes, st)))
         return rc;
       mark(r, "latent_attn");
       if ((rc = nvc_linear(ctx, olat, lw, w.kvp, w.w_uv, w.kvp, (int64_t)w.vdp * w.kvp, ao, vw, w.vdp, dt, odt, N, w.vdp, w.kvp, m.heads,

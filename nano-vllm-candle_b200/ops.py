@@ -424,12 +424,15 @@ def moe_combine(ctx, y, pos, w, shared=None, gate=None) -> torch.Tensor:
     return out
 
 
-def latent_attn_paged(ctx, q, cache, block_tables, context_lens, cu_seqlens, max_qlen: int, block_size: int, scale: float):
+def latent_attn_paged(ctx, q, cache, block_tables, context_lens, cu_seqlens, max_qlen: int, block_size: int, scale: float,
+                      workspace: Optional[torch.Tensor] = None):
     """q: [rows, heads, D]; cache: [slots, >= D]; returns the attended latents [rows, heads, D]."""
     rows, heads, D = q.shape
     out = torch.empty_like(q)
     B = context_lens.numel()
     check(ctx.l.nvc_latent_attn_paged(ctx.h, _ptr(q), heads * D, _ptr(cache), cache.stride(0), _ptr(block_tables),
                                       block_tables.stride(0), _ptr(context_lens), _ptr(cu_seqlens), B, max_qlen, heads, D, D,
-                                      block_size, scale, _ptr(out), heads * D, _dt(q), _stream()), "nvc_latent_attn_paged", ctx.h)
+                                      block_size, scale, _ptr(out), heads * D, _dt(q), _ptr(workspace),
+                                      workspace.numel() * workspace.element_size() if workspace is not None else 0, _stream()),
+          "nvc_latent_attn_paged", ctx.h)
     return out

@@ -225,6 +225,23 @@ def test_latent_attention_mixed_batch(ctx, ops, dt, heads, D, bs):
     assert torch.allclose(out.float().cpu(), want, **tol(dt))
 
 
+@pytest.mark.parametrize("heads,D", [(5, 64), (16, 128), (40, 128), (70, 64)])
+def test_latent_attention_decode_with_keys_split_over_ctas(ctx, ops, heads, D):
+    """A small decode batch with a workspace: the keys of a sequence are walked by several CTAs and merged."""
+    g = torch.Generator().manual_seed(17)
+    bs, dt = 32, torch.bfloat16
+    ctx_lens = [1, 63, 64, 65, 700, 129]
+    cs = [torch.randn(n, D, generator=g).to(dt).float() for n in ctx_lens]
+    cache, bt, cl = paged(cs, bs, 48, dt, 18)
+    q = torch.randn(len(ctx_lens), heads, D, generator=g).to(dt).float()
+    ws = torch.full((4 << 20,), float("nan"), dtype=torch.float32, device=DEV)
+    out = ops.latent_attn_paged(ctx, q.to(dt).to(DEV), cache, bt, cl, None, 1, bs, 0.2, workspace=ws)
+    plain = ops.latent_attn_paged(ctx, q.to(dt).to(DEV), cache, bt, cl, None, 1, bs, 0.2)
+    want = torch.cat([attn_want(q[i:i + 1], c, 0.2) for i, c in enumerate(cs)])
+    assert torch.allclose(out.float().cpu(), want, **tol(dt))
+    assert torch.allclose(out.float(), plain.float(), rtol=1e-2, atol=1e-2)
+
+
 @pytest.mark.parametrize("dt", DTS)
 def test_latent_attention_decode_rows_without_cu_seqlens(ctx, ops, dt):
     g = torch.Generator().manual_seed(13)
