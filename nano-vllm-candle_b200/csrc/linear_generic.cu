@@ -106,13 +106,14 @@ __device__ __forceinline__ void mma16816(float* d, const uint32_t* a, uint32_t b
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <typename TC>
-__global__ void __launch_bounds__(128)
+// BT x BT output tile, 2 * BT threads: BT / 32 x 2 warps of 32 x BT / 2
+template <typename TC, int BT>
+__global__ void __launch_bounds__(2 * BT)
 linear_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, int64_t sa, const int32_t* __restrict__ a_rows,
                   const __nv_bfloat16* __restrict__ W, int ldw, int64_t sw, TC* __restrict__ C, int ldc, int64_t sc,
                   const int32_t* __restrict__ offsets, int groups, int M, int N, int K, int act) {
-  __shared__ __align__(128) uint8_t sA[2][TM * MROW];
-  __shared__ __align__(128) uint8_t sW[2][TN * MROW];
+  __shared__ __align__(128) uint8_t sA[2][BT * MROW];
+  __shared__ __align__(128) uint8_t sW[2][BT * MROW];
   pdl_trigger();
   pdl_wait();
   int row0, row_end;
@@ -120,31 +121,32 @@ linear_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, int64_t sa, cons
     int t = blockIdx.x, g = 0, base = 0;
     for (; g < groups; ++g) {
       base = offsets[g];
-      const int tiles = (offsets[g + 1] - base + TM - 1) / TM;
+      const int tiles = (offsets[g + 1] - base + BT - 1) / BT;
       if (t < tiles) break;
       t -= tiles;
     }
     if (g == groups) return;
-    row0 = base + t * TM;
+    row0 = base + t * BT;
     row_end = offsets[g + 1];
     W += (int64_t)g * sw;
   } else {
-    row0 = blockIdx.x * TM;
+    row0 = blockIdx.x * BT;
     row_end = M;
     A += (int64_t)blockIdx.z * sa;
     W += (int64_t)blockIdx.z * sw;
     C += (int64_t)blockIdx.z * sc;
   }
-  const int col0 = blockIdx.y * TN;
+  const int col0 = blockIdx.y * BT;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
-  // loader: 64 rows x 4 chunks of 16 bytes per operand and stage; thread -> rows (tid / 4) and (tid / 4 + 32), chunk tid % 4
+  constexpr int WNT = BT / 2, NP = WNT / 16, NT = WNT / 8;   // warp tile 32 x WNT
+  const int wm = (warp >> 1) * 32, wn = (warp & 1) * WNT;
+  // loader: BT rows x 4 chunks of 16 bytes per operand and stage; thread -> rows (tid / 4) and (tid / 4 + BT / 2), chunk tid % 4
   const int lc = tid & 3;
   const __nv_bfloat16* a_src[2];
   const __nv_bfloat16* w_src[2];
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
-    const int r = (tid >> 2) + 32 * i;
+    const int r = (tid >> 2) + (BT / 2) * i;
     const int ar = row0 + r;
     a_src[i] = ar < row_end ? A + (int64_t)(a_rows ? a_rows[ar] : ar) * lda : nullptr;
     w_src[i] = col0 + r < N ? W + (int64_t)(col0 + r) * ldw : nullptr;
@@ -153,7 +155,7 @@ linear_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, int64_t sa, cons
     const int k = kb * MK + lc * 8;
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-      const int r = (tid >> 2) + 32 * i;
+      const int r = (tid >> 2) + (BT / 2) * i;
       const uint32_t off = r * MROW + lc * 16;
       // K is a multiple of 8: a chunk is inside the row or entirely past its end (zero-filled)
       cp16(smem_u32(sA[stage]) + off, a_src[i] && k < K ? (const void*)(a_src[i] + k) : (const void*)A, a_src[i] && k < K ? 16u : 0u);
@@ -161,11 +163,11 @@ linear_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, int64_t sa, cons
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  float acc[2][4][4];
+  float acc[2][NT][4];
 #pragma unroll
   for (int i = 0; i < 2; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
+    for (int j = 0; j < NT; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
   const int nkb = (K + MK - 1) / MK;
   load(0, 0);
   for (int kb = 0; kb < nkb; ++kb) {
@@ -181,7 +183,7 @@ linear_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, int64_t sa, cons
       for (int mt = 0; mt < 2; ++mt)
         ldsm4(a_base + (wm + mt * 16 + (lane & 15)) * MROW + (ks * 2 + (lane >> 4)) * 16, af[mt][0], af[mt][1], af[mt][2], af[mt][3]);
 #pragma unroll
-      for (int np = 0; np < 2; ++np) {
+      for (int np = 0; np < NP; ++np) {
         uint32_t b0, b1, b2, b3;
         ldsm4(w_base + (wn + np * 16 + (lane & 7) + ((lane >> 4) << 3)) * MROW + (ks * 2 + ((lane >> 3) & 1)) * 16, b0, b1, b2, b3);
 #pragma unroll
@@ -201,7 +203,7 @@ linear_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, int64_t sa, cons
       const int r = row0 + wm + mt * 16 + quad + 8 * hf;
       if (r >= row_end) continue;
 #pragma unroll
-      for (int nt = 0; nt < 4; ++nt) {
+      for (int nt = 0; nt < NT; ++nt) {
         const int c = col0 + wn + nt * 8 + 2 * tq;
         float v0 = acc[mt][nt][2 * hf], v1 = acc[mt][nt][2 * hf + 1];
         if (act == NVC_ACT_RELU2) { v0 = fmaxf(v0, 0.f); v0 *= v0; v1 = fmaxf(v1, 0.f); v1 *= v1; }
@@ -223,14 +225,27 @@ bool mma_ok(int in_dtype, const void* A, int lda, int64_t sa, const void* W, int
          ((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0;
 }
 
-template <typename TC>
-int launch_mma(nvc_ctx* ctx, dim3 grid, void* stream, const void* A, int lda, int64_t sa, const int32_t* a_rows, const void* W, int ldw,
-               int64_t sw, void* C, int ldc, int64_t sc, const int32_t* offsets, int groups, int M, int N, int K, int act) {
-  NVC_CUDA_CHECK(ctx, nvc_launch(ctx, linear_mma_kernel<TC>, grid, dim3(128), 0, nvc_stream(stream),
+template <typename TC, int BT>
+int launch_mma_t(nvc_ctx* ctx, dim3 grid, void* stream, const void* A, int lda, int64_t sa, const int32_t* a_rows, const void* W, int ldw,
+                 int64_t sw, void* C, int ldc, int64_t sc, const int32_t* offsets, int groups, int M, int N, int K, int act) {
+  NVC_CUDA_CHECK(ctx, nvc_launch(ctx, linear_mma_kernel<TC, BT>, grid, dim3(2 * BT), 0, nvc_stream(stream),
                                  reinterpret_cast<const __nv_bfloat16*>(A), lda, sa, a_rows, reinterpret_cast<const __nv_bfloat16*>(W), ldw,
                                  sw, reinterpret_cast<TC*>(C), ldc, sc, offsets, groups, M, N, K, act));
   ctx->launches++;
   return NVC_OK;
+}
+
+// 128 x 128 tiles when there are enough rows and columns to fill the GPU with them (prefill-sized products), else 64 x 64;
+// `batch` is the z extent of a plain / batched launch (1 for a grouped one)
+template <typename TC>
+int launch_mma(nvc_ctx* ctx, int batch, void* stream, const void* A, int lda, int64_t sa, const int32_t* a_rows, const void* W, int ldw,
+               int64_t sw, void* C, int ldc, int64_t sc, const int32_t* offsets, int groups, int M, int N, int K, int act) {
+  const bool big = N >= 128 && (int64_t)(M / 128 + groups) * ((N + 127) / 128) * batch >= ctx->num_sms;
+  const int BT = big ? 128 : 64;
+  const int mt = offsets ? M / BT + groups : (M + BT - 1) / BT;     // grouped: every group may end with a partial tile
+  const dim3 grid(mt, (N + BT - 1) / BT, batch);
+  if (big) return launch_mma_t<TC, 128>(ctx, grid, stream, A, lda, sa, a_rows, W, ldw, sw, C, ldc, sc, offsets, groups, M, N, K, act);
+  return launch_mma_t<TC, 64>(ctx, grid, stream, A, lda, sa, a_rows, W, ldw, sw, C, ldc, sc, offsets, groups, M, N, K, act);
 }
 
 template <typename T, typename TC>
@@ -248,8 +263,8 @@ int dispatch(nvc_ctx* ctx, dim3 grid, void* stream, int in_dtype, int out_dtype,
              int groups, int M, int N, int K, int act) {
   if (mma_ok(in_dtype, A, lda, sa, W, ldw, sw, K)) {
     if (out_dtype == NVC_DT_F32)
-      return launch_mma<float>(ctx, grid, stream, A, lda, sa, a_rows, W, ldw, sw, C, ldc, sc, offsets, groups, M, N, K, act);
-    return launch_mma<__nv_bfloat16>(ctx, grid, stream, A, lda, sa, a_rows, W, ldw, sw, C, ldc, sc, offsets, groups, M, N, K, act);
+      return launch_mma<float>(ctx, (int)grid.z, stream, A, lda, sa, a_rows, W, ldw, sw, C, ldc, sc, offsets, groups, M, N, K, act);
+    return launch_mma<__nv_bfloat16>(ctx, (int)grid.z, stream, A, lda, sa, a_rows, W, ldw, sw, C, ldc, sc, offsets, groups, M, N, K, act);
   }
   if (in_dtype == NVC_DT_F32) {
     NVC_REQUIRE(ctx, out_dtype == NVC_DT_F32, NVC_EINVAL, "fp32 operands give an fp32 result");

@@ -107,6 +107,29 @@ def test_linear_any_shape(ctx, ops, dt, shape):
     assert torch.allclose(out.cpu(), torch.relu(want) ** 2, rtol=2e-5, atol=2e-5)
 
 
+def test_linear_large_shapes_take_the_wide_tiles(ctx, ops):
+    """Enough rows and columns for one 128 x 128 tile per SM: plain, batched and grouped, with ragged edges."""
+    g = torch.Generator().manual_seed(23)
+    dt = torch.bfloat16
+    A, W = torch.randn(5000, 72, generator=g).to(dt), (torch.randn(520, 72, generator=g) * 0.1).to(dt)
+    out = ops.linear(ctx, A.to(DEV), W.to(DEV), out_dtype=torch.float32)
+    assert torch.allclose(out.cpu(), A.float() @ W.float().T, rtol=2e-3, atol=2e-3)
+    A3, W3 = torch.randn(5, 4000, 40, generator=g).to(dt), (torch.randn(5, 136, 40, generator=g) * 0.2).to(dt)
+    out = ops.linear(ctx, A3.to(DEV), W3.to(DEV))
+    assert torch.allclose(out.float().cpu(), torch.einsum("bmk,bnk->bmn", A3.float(), W3.float()), **tol(dt))
+    sizes = [3000, 0, 129, 9000, 7871]
+    offsets = torch.tensor([0] + list(torch.tensor(sizes).cumsum(0)), dtype=torch.int32)
+    rows = int(offsets[-1])
+    Ag, Wg = torch.randn(700, 48, generator=g).to(dt), (torch.randn(5, 130, 48, generator=g) * 0.2).to(dt)
+    a_rows = torch.randint(0, 700, (rows,), generator=g, dtype=torch.int32)
+    out = ops.linear_grouped(ctx, Ag.to(DEV), a_rows.to(DEV), Wg.to(DEV), offsets.to(DEV), rows, out_dtype=torch.float32, act=ops.ACT_RELU2)
+    want = torch.zeros(rows, 130)
+    for e in range(5):
+        lo, hi = int(offsets[e]), int(offsets[e + 1])
+        want[lo:hi] = torch.relu(Ag.float()[a_rows[lo:hi].long()] @ Wg[e].float().T) ** 2
+    assert torch.allclose(out.cpu(), want, rtol=2e-3, atol=2e-3)
+
+
 @pytest.mark.parametrize("dt", DTS)
 def test_linear_batched_per_head(ctx, ops, dt):
     g = torch.Generator().manual_seed(6)
