@@ -80,6 +80,7 @@ struct KaruzenBody : nvc_model_body {
   size_t esz = 2;
   int Wp = 0, Vp = 0;
   bool use_tc = true;                  // tcgen05 GEMMs for the plain products of the bf16 mode
+  bool use_flash = true;               // tcgen05 paged-prefill kernel for long prompt portions (bf16, padded latent of 128)
   std::vector<LayerW> L;
   std::vector<void*> cache;            // per run: [slots, kvp]
   int kvp_max = 0;
@@ -169,6 +170,7 @@ struct KaruzenBody : nvc_model_body {
     dt = r->dtype;
     esz = dt == NVC_DT_F32 ? 4 : 2;
     use_tc = dt == NVC_DT_BF16 && !(getenv("NVC_KARUZEN_TC") && atoi(getenv("NVC_KARUZEN_TC")) == 0);
+    use_flash = use_tc && !(getenv("NVC_KARUZEN_FLASH") && atoi(getenv("NVC_KARUZEN_FLASH")) == 0);
     runs = cfg.runs();
     Wp = pad64(cfg.width);
     Vp = pad64(cfg.vocab);
@@ -395,6 +397,16 @@ struct KaruzenBody : nvc_model_body {
     return nvc_linear(r->ctx, A, lda, 0, Wt, K, 0, C, ldc, 0, dt, dt == NVC_DT_F32 ? NVC_DT_F32 : out_dt, M, N, K, 1, act, r->stream);
   }
 
+  // Prompt portions of this step go through the tcgen05 paged-prefill kernel when the storage is bf16, the padded latent is
+  // that kernel's head size and the block size is one it tiles; shorter portions stay with the latent kernel (a 128-row
+  // query tile per head would be mostly empty).
+  static constexpr int kFlashMinChunk = 64;
+  bool flash_portions(const nvc_runner* r, const nvc_step_shape& s, int kvp) const {
+    const int bs = r->opt.kvcache_block_size;
+    return use_flash && !s.decode && kvp == 128 && s.num_decode < s.B && s.max_chunk >= kFlashMinChunk &&
+           (bs == 16 || bs == 32 || bs == 64 || bs % 128 == 0);
+  }
+
   int tap(nvc_runner* r, int run, int N) {
     const size_t need = (size_t)(run + 1) * N * cfg.width;
     NVC_REQUIRE(r->ctx, need <= tap_cap, NVC_ENOMEM, "residual tap buffer too small");
@@ -449,10 +461,27 @@ struct KaruzenBody : nvc_model_body {
                            m.heads, NVC_ACT_NONE, st)))
         return rc;
       mark(r, "absorb_uk");
-      if ((rc = nvc_latent_attn_paged(ctx, qabs, lw, cache[k], w.kvp, r->d_bt, r->max_blocks_cap, r->d_ctx, s.decode ? nullptr : r->d_cu,
-                                      s.B, s.decode ? 1 : s.max_seqlen, m.heads, m.kv_rank, w.kvp, r->opt.kvcache_block_size, m.scale,
-                                      olat, lw, dt, attn_ws, attn_ws_bytes, st)))
+      if (flash_portions(r, s, w.kvp)) {
+        // Long prompt portions: in the absorbed form a layer is multi-query attention with ONE key / value head whose
+        // key and value are both the cached latent row, so the tcgen05 paged-prefill kernel runs it unchanged (k = v =
+        // this run's pool, head size = the padded latent width).  One-token sequences of a mixed step come first in the
+        // batch and keep the decode path of the latent kernel.
+        const int nd = s.num_decode, cap = r->max_blocks_cap;
+        const nvc_bf16* qb = reinterpret_cast<const nvc_bf16*>(qabs);
+        nvc_bf16* ob = reinterpret_cast<nvc_bf16*>(olat);
+        const nvc_bf16* pool = reinterpret_cast<const nvc_bf16*>(cache[k]);
+        if (nd > 0 && (rc = nvc_latent_attn_paged(ctx, qabs, lw, cache[k], w.kvp, r->d_bt, cap, r->d_ctx, nullptr, nd, 1, m.heads, m.kv_rank,
+                                                  w.kvp, r->opt.kvcache_block_size, m.scale, olat, lw, dt, attn_ws, attn_ws_bytes, st)))
+          return rc;
+        if ((rc = nvc_prefill_attn_paged(ctx, qb + (size_t)nd * lw, lw, pool, pool, r->d_bt + (size_t)nd * cap, cap, r->d_ctx + nd,
+                                         nd ? r->d_cu2 : r->d_cu, s.B - nd, s.N - nd, s.max_chunk, m.heads, 1, w.kvp,
+                                         r->opt.kvcache_block_size, r->opt.num_kvcache_blocks, m.scale, ob + (size_t)nd * lw, st)))
+          return rc;
+      } else if ((rc = nvc_latent_attn_paged(ctx, qabs, lw, cache[k], w.kvp, r->d_bt, r->max_blocks_cap, r->d_ctx,
+                                             s.decode ? nullptr : r->d_cu, s.B, s.decode ? 1 : s.max_seqlen, m.heads, m.kv_rank, w.kvp,
+                                             r->opt.kvcache_block_size, m.scale, olat, lw, dt, attn_ws, attn_ws_bytes, st))) {
         return rc;
+      }
       mark(r, "latent_attn");
       if ((rc = nvc_linear(ctx, olat, lw, w.kvp, w.w_uv, w.kvp, (int64_t)w.vdp * w.kvp, ao, vw, w.vdp, dt, odt, N, w.vdp, w.kvp, m.heads,
                            NVC_ACT_NONE, st)))

@@ -641,6 +641,7 @@ int prefill_impl(nvc_runner* r, const int32_t* ids, const int32_t* positions, co
   if (r->body) {
     nvc_step_shape sh;
     sh.N = N; sh.B = B; sh.max_seqlen = max_seqlen; sh.rows = rows;
+    sh.num_decode = num_decode; sh.max_chunk = max_seqlen_chunks;
     rc = r->body->forward(r, sh);
     if (rc == NVC_OK && !use_armed) rc = body_tokens(r, B);
     r->sampling_armed = false;

@@ -22,6 +22,10 @@ struct nvc_step_shape {
   int max_seqlen = 1;     // longest q_len of the step
   bool decode = false;    // every sequence has one query row and d_cu was not uploaded
   int rows = 0;           // rows whose logits are computed (d_last_rows holds their indices; decode: rows == B, identity)
+  // mixed step: the first num_decode sequences have one query row each; d_cu2 holds the cu_seqlens of the others relative to
+  // their first row (when 0 < num_decode < B), and max_chunk is the longest q_len among them
+  int num_decode = 0;
+  int max_chunk = 1;
 };
 
 // A model family behind the runner.  Implementations: model_karuzen.cu.

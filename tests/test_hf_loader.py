@@ -313,3 +313,28 @@ def test_runner_from_hf_dir_matches_from_weights(ctx, tmp_path, layout):
     finally:
         a.close()
         b.close()
+
+
+@pytest.mark.gpu
+def test_registry_runner_loads_a_qwen3_directory(ctx, tmp_path):
+    """ModelRunner.from_dir picks the family by config.json: a Qwen3 directory gives the built-in Qwen3 body, with the
+    same tokens as Qwen3ModelRunner.from_hf_dir."""
+    cfg = O.MODEL_CONFIGS["qwen3-tiny"]
+    w = synth.make_weights(cfg, seed=4, norm_jitter=0.1)
+    _write_config(tmp_path, cfg, head_dim=cfg.head_dim, tie_word_embeddings=False)
+    save_file({k: v.to(torch.bfloat16).contiguous() for k, v in w.items()}, str(tmp_path / "model.safetensors"))
+    kw = dict(num_kvcache_blocks=16, kvcache_block_size=16, max_num_seqs=2, max_num_batched_tokens=256, max_model_len=256)
+    a = eng.ModelRunner.from_dir(ctx, str(tmp_path), **kw)
+    b = eng.Qwen3ModelRunner.from_hf_dir(ctx, str(tmp_path), **kw)
+    try:
+        assert a.architecture == "Qwen3ForCausalLM" and a.eos_id == cfg.eos_token_id and a.vocab_size == cfg.vocab_size
+        prompts = synth.make_prompts(2, 21, cfg.vocab_size, 6)
+        outs = []
+        for r in (a, b):
+            e = eng.LLMEngine(eng.Scheduler(eng.SchedulerConfig(2, 256, cfg.eos_token_id, 16, 16)), r, greedy=True)
+            outs.append([o.token_ids for o in e.generate(prompts, eng.SamplingParams(1.0, 6, True))])
+            e.close()
+        assert outs[0] == outs[1] and all(len(t) == 6 for t in outs[0])
+    finally:
+        a.close()
+        b.close()

@@ -192,6 +192,36 @@ def test_other_sizes(dtype):
         r.close()
 
 
+def cfg_c():
+    """Every latent pads to 128 numbers, the width at which long prompt portions of the bf16 mode run on the tcgen05
+    paged-prefill kernel (as multi-query attention over the latent rows); head counts that divide nothing."""
+    return K.make_config(vocab=160, width=128, layers=[
+        {"type": "latent_attention", "mixer": K.mixer_cfg(3, 32, 16, 128, 48, 0.2), "mlp": K.dense_cfg(96)},
+        {"type": "latent_attention", "mixer": K.mixer_cfg(5, 16, 24, 100, 32, 0.3), "mlp": None},
+    ], loop={"start": 0, "stop": 2, "times": 2})
+
+
+@pytest.mark.parametrize("flash", ["1", "0"])
+def test_long_portions_beside_decoded_tokens(monkeypatch, flash):
+    """Portions of 64 tokens and more - whole prompts, behind a cached prefix that ends inside a page, beside one-token
+    sequences of the same step - against the oracle, with the tcgen05 route on and off (the two must agree with the
+    oracle alike: which kernel computed a position depends on the schedule)."""
+    monkeypatch.setenv("NVC_KARUZEN_FLASH", flash)
+    r = Rig(cfg_c(), "bfloat16", blocks=48, seed=12)
+    try:
+        V = r.cfg["vocab"]
+        pr = {"a": toks(333, V, 60), "b": toks(131, V, 61), "c": toks(70, V, 62), "d": toks(5, V, 63)}
+        sched = [[("a", 129), ("d", 1)], [("d", 1), ("a", 64), ("b", 77)], [("d", 1), ("a", 1), ("b", 3), ("c", 70)],
+                 [("d", 1), ("b", 51), ("a", 139)], [("d", 1)]]
+        assert all(sum(n for s in sched for k, n in s if k == name) == len(p) for name, p in pr.items())
+        r.check(pr, sched)
+        # a whole prompt in one portion, then the same prompt cut after nine tokens (prefix shorter than a page)
+        r.check({"w": toks(200, V, 64)}, [[("w", 200)]])
+        r.check({"w": toks(200, V, 64)}, [[("w", 9)], [("w", 191)]])
+    finally:
+        r.close()
+
+
 @pytest.mark.parametrize("dtype,chunked", [("float32", False), ("float32", True), ("bfloat16", True)])
 def test_greedy_generation_through_the_scheduler(dtype, chunked):
     """LLMEngine.generate: the engine's own admission, paged prefill, graph-captured decode steps.  Every generated token
