@@ -179,6 +179,19 @@ int nvc_gemm_bf16(nvc_ctx* ctx, const nvc_bf16* A, int lda, const nvc_bf16* W, v
 int nvc_gemm_bf16_silu_mul(nvc_ctx* ctx, const nvc_bf16* A, int lda, const nvc_bf16* W_gu16, nvc_bf16* act,
                            int ldc, int M, int I, int K, void* stream);
 
+/* C = act(A W^T) on the tcgen05 kernels with the activation in the epilogue; act: NVC_ACT_NONE or NVC_ACT_RELU2
+ * (max(z, 0)^2 on the fp32 accumulators).  Shapes as nvc_gemm_bf16. */
+int nvc_gemm_bf16_act(nvc_ctx* ctx, const nvc_bf16* A, int lda, const nvc_bf16* W, void* C, int ldc, int out_dtype, int M,
+                      int Nout, int K, int act, void* stream);
+
+/* Grouped product on the tcgen05 kernel: the rows of A are sorted by group, every group starts at a multiple of 128 rows
+ * (nvc_moe_sort_padded), W = [groups][Nout][K] and C[r] = act(A[r] . W[tile_group[r / 128]]^T); tiles whose tile_group
+ * entry is negative are skipped.  M_cap (a multiple of 128) is the host's upper bound of the padded row count: the
+ * launch depends on no device value and replays inside a CUDA graph.  Rows of A in a group's padding may hold anything;
+ * their rows of C are written and mean nothing.  act: NVC_ACT_NONE or NVC_ACT_RELU2. */
+int nvc_gemm_bf16_grouped(nvc_ctx* ctx, const nvc_bf16* A, int lda, const nvc_bf16* W, void* C, int ldc, int out_dtype,
+                          int M_cap, int Nout, int K, const int32_t* tile_group, int groups, int act, void* stream);
+
 /* The same fused kernel with the tanh form of gelu on the gate (gated feed-forward of the Karuzen family):
  *   act[M, I] = gelu_tanh(A Wgate^T) * (A Wup^T),  gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))),
  * hardware tanh on the fp32 accumulators; W_gu16 interleaved as for nvc_gemm_bf16_silu_mul. */
@@ -333,6 +346,16 @@ int nvc_moe_route_logits(nvc_ctx* ctx, const float* z, int ldz, const float* cor
  * pair at each sorted position), pos [N * top] (sorted position of pair n * top + t). */
 int nvc_moe_sort(nvc_ctx* ctx, const int32_t* topk_idx, int N, int top, int E, int32_t* offsets, int32_t* src_rows, int32_t* pos,
                  void* stream);
+/* The same sort with every expert's group starting at a multiple of `align` rows (the layout of nvc_gemm_bf16_grouped,
+ * align = 128): offsets[e] are the padded starts (offsets[E] = padded row count), src_rows has -1 in the padding rows,
+ * pos points into the padded layout, and tile_group [tiles_cap] (optional) names the expert of every `align`-row tile, -1
+ * behind the last group.  tiles_cap * align >= N * top + E * (align - 1); src_rows needs tiles_cap * align entries. */
+int nvc_moe_sort_padded(nvc_ctx* ctx, const int32_t* topk_idx, int N, int top, int E, int align, int32_t* offsets, int32_t* src_rows,
+                        int32_t* pos, int32_t* tile_group, int tiles_cap, void* stream);
+/* out[r, :width] = in[src_rows[r], :width] for r < min(rows_cap, *num_rows) (num_rows: a count in device memory), zeros
+ * where src_rows[r] < 0.  bf16 rows, width and strides multiples of 8. */
+int nvc_gather_rows_bf16(nvc_ctx* ctx, const nvc_bf16* in, int ld_in, const int32_t* src_rows, const int32_t* num_rows, nvc_bf16* out,
+                         int ld_out, int rows_cap, int width, void* stream);
 /* out[n, :H] = sum_t topk_w[n, t] * y[pos[n * top + t], :H] + gate[n] * shared[n, :H]   (fp32; shared / gate optional). */
 int nvc_moe_combine(nvc_ctx* ctx, const void* y, int y_dtype, int ldy, const int32_t* pos, const float* topk_w, int top,
                     const void* shared, int shared_dtype, int lds, const float* gate, float* out, int ldo, int N, int H,

@@ -101,6 +101,10 @@ def _declare(l: C.CDLL) -> None:
         "nvc_moe_route": [_vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _f, _vp, _vp, _vp, _i, _i, _vp],
         "nvc_moe_route_logits": [_vp, _vp, _i, _vp, _i, _i, _f, _i, _vp, _vp, _vp, _i, _vp],
         "nvc_moe_sort": [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp],
+        "nvc_moe_sort_padded": [_vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp],
+        "nvc_gather_rows_bf16": [_vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _vp],
+        "nvc_gemm_bf16_act": [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+        "nvc_gemm_bf16_grouped": [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _i, _vp],
         "nvc_moe_combine": [_vp, _vp, _i, _i, _vp, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _vp],
         "nvc_latent_attn_paged": [_vp, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _i, _i, _vp, _sz, _vp],
         "nvc_debug_set": [_i, _i],

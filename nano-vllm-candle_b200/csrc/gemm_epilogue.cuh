@@ -11,7 +11,8 @@
 // NVC_EPI_TRANSPOSE (pair kernel, persistent schedule): the operands are swapped by the host - the kernel's "A" rows are
 // weight rows, its "W" rows are tokens - and the epilogue stores its accumulator row r as COLUMN r of C: lm_head at decode
 // batch sizes, where 64 tokens would fill a quarter of a 256-row MMA and only one CTA of the pair would hold valid rows.
-enum { NVC_EPI_NONE = 0, NVC_EPI_SILU_MUL = 1, NVC_EPI_TRANSPOSE = 2, NVC_EPI_QK_NORM_ROPE = 3, NVC_EPI_GELU_TANH_MUL = 4 };
+// NVC_EPI_RELU2: C = max(acc, 0)^2, element by element (the experts of the Karuzen family), any output type.
+enum { NVC_EPI_NONE = 0, NVC_EPI_SILU_MUL = 1, NVC_EPI_TRANSPOSE = 2, NVC_EPI_QK_NORM_ROPE = 3, NVC_EPI_GELU_TANH_MUL = 4, NVC_EPI_RELU2 = 5 };
 
 // the gated epilogues write half as many columns as the accumulator has
 __host__ __device__ __forceinline__ bool nvc_epi_gated(int epi) { return epi == NVC_EPI_SILU_MUL || epi == NVC_EPI_GELU_TANH_MUL; }
@@ -31,6 +32,16 @@ __device__ __forceinline__ void nvc_gated16(int epi, const float* f, float* o) {
       asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * (z + 0.044715f * z * z * z)));
       o[j] = 0.5f * z * (1.0f + t) * f[16 + j];
     }
+  }
+}
+// the element-wise epilogues on 32 accumulator columns: squared relu, or a copy (a select per element keeps both arrays in
+// registers; choosing between two array pointers would not)
+__device__ __forceinline__ void nvc_unary32(int epi, const float* f, float* o) {
+  const bool r2 = epi == NVC_EPI_RELU2;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    const float r = fmaxf(f[j], 0.f);
+    o[j] = r2 ? r * r : f[j];
   }
 }
 #endif
@@ -76,8 +87,10 @@ __device__ __forceinline__ void emit32(void* C, int out_f32, int epi, int64_t ro
       store16(C, 0, row_off + (n0 >> 1), o);
     }
   } else {
-    if (n0 < N) store16(C, out_f32, row_off + n0, f);
-    if (n0 + 16 < N) store16(C, out_f32, row_off + n0 + 16, f + 16);
+    float g[32];
+    nvc_unary32(epi, f, g);
+    if (n0 < N) store16(C, out_f32, row_off + n0, g);
+    if (n0 + 16 < N) store16(C, out_f32, row_off + n0 + 16, g + 16);
   }
 }
 
@@ -125,13 +138,18 @@ struct RowStage {
       nvc_gated16(epi, f, o);
       put(lane, pack8(o));
       put(lane, pack8(o + 8));
-    } else if (out_f32) {
+      if (filled == 128) flush(lane);
+      return;
+    }
+    float g[32];
+    nvc_unary32(epi, f, g);
+    if (out_f32) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) put(lane, make_uint4(__float_as_uint(f[4 * j]), __float_as_uint(f[4 * j + 1]),
-                                                       __float_as_uint(f[4 * j + 2]), __float_as_uint(f[4 * j + 3])));
+      for (int j = 0; j < 8; ++j) put(lane, make_uint4(__float_as_uint(g[4 * j]), __float_as_uint(g[4 * j + 1]),
+                                                       __float_as_uint(g[4 * j + 2]), __float_as_uint(g[4 * j + 3])));
     } else {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) put(lane, pack8(f + 8 * j));
+      for (int j = 0; j < 4; ++j) put(lane, pack8(g + 8 * j));
     }
     if (filled == 128) flush(lane);
   }

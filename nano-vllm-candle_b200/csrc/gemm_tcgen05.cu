@@ -61,7 +61,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                          void* __restrict__ C, int ldc, int out_f32, int M, int N, int k_blocks_total,
                          int k_blocks_per_split, int a_box_rows, int prefetch_w, int ks_cluster, int epi, float* __restrict__ ws,
-                         int* __restrict__ counters, long long* __restrict__ trace) {
+                         int* __restrict__ counters, long long* __restrict__ trace, const int32_t* __restrict__ tile_group,
+                         int group_w_rows) {
   using cfg = Cfg<BN, KPS>;
   // optional phase timestamps of CTA (0,0,0) (tools/gemm_microbench.py); NULL in production
   const bool tr = trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
@@ -140,15 +141,24 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   }
   pdl_wait();      // everything above (barrier init, TMEM alloc, descriptor prefetch, first W loads) overlapped the predecessor
   if (tr && threadIdx.x == 0) trace[1] = clock64();
+  // Grouped product (tile_group != NULL): the rows of A are sorted by group, every group starts at a multiple of BM, and
+  // m-tile t multiplies with the weight rows of group tile_group[t] ([group][N][K] in W).  The table is written by an
+  // earlier kernel of the stream, so it is read after the wait (past L1).  A negative entry marks a tile behind the last
+  // group: its CTA computes nothing and only tears down.
+  const int grp = tile_group ? __ldcg(tile_group + m_tile) : 0;
+  const bool skip = grp < 0;
+  const int w_row0 = n_tile * BN + (tile_group ? grp * group_w_rows : 0);
 
-  if (warp == 0 || warp == 2) {
+  if (skip) {
+    // nothing to load or multiply
+  } else if (warp == 0 || warp == 2) {
     // ------------------------------------------------------------ TMA producers
     const bool is_a = warp == 0;
     // bytes ONE box delivers into this CTA per k-block (A: all CL slices land here)
     const uint32_t sub_bytes = is_a ? (uint32_t)a_box_rows * CL * (BK * 2) : (uint32_t)cfg::kBytesB;
     const uint32_t sub_stride = is_a ? (uint32_t)cfg::kBytesA : (uint32_t)cfg::kBytesB;
     const CUtensorMap* map = is_a ? &tma_a : &tma_b;
-    const int row0 = is_a ? m_tile * BM + (int)cta_rank * a_box_rows : n_tile * BN;
+    const int row0 = is_a ? m_tile * BM + (int)cta_rank * a_box_rows : w_row0;
     const uint32_t off = is_a ? cta_rank * (uint32_t)a_box_rows * (BK * 2) : (uint32_t)(KPS * cfg::kBytesA);
     for (int it = is_a ? 0 : w_pre; it < num_it; ++it) {
       const int s = it % cfg::kStages;
@@ -213,7 +223,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       __syncwarp();
     }
   }
-  if (warp >= 2) {
+  if (warp >= 2 && !skip) {
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;                 // TMEM lane quadrant this warp may access
     const int r = q * 32 + lane;            // row inside the tile
@@ -403,7 +413,8 @@ int make_tma_2d(nvc_ctx* ctx, CUtensorMap* map, const void* base, uint64_t inner
 
 template <int BN, int KPS, int CL>
 int launch(nvc_ctx* ctx, const nvc_bf16* A, int lda, const nvc_bf16* W, void* C, int ldc, int out_f32, int M,
-           int N, int K, int splits, int ks_cluster, int epi, cudaStream_t stream, long long* trace) {
+           int N, int K, int splits, int ks_cluster, int epi, cudaStream_t stream, long long* trace,
+           const int32_t* tile_group = nullptr, int groups = 1) {
   using cfg = Cfg<BN, KPS>;
   CUtensorMap ta, tb;
   // a single partial m-tile only needs the rows that exist (rounded to the 8-row swizzle atom per
@@ -411,7 +422,7 @@ int launch(nvc_ctx* ctx, const nvc_bf16* A, int lda, const nvc_bf16* W, void* C,
   const int a_rows = M >= BM ? BM : ((M + 8 * CL - 1) / (8 * CL)) * (8 * CL);
   int rc = make_tma_2d(ctx, &ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, a_rows / CL);
   if (rc) return rc;
-  rc = make_tma_2d(ctx, &tb, W, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, BK, BN);
+  rc = make_tma_2d(ctx, &tb, W, (uint64_t)K, (uint64_t)N * groups, (uint64_t)K * 2, BK, BN);
   if (rc) return rc;
   const int kb_total = K / BK;
   const int kb_per = (kb_total + splits - 1) / splits;
@@ -428,8 +439,8 @@ int launch(nvc_ctx* ctx, const nvc_bf16* A, int lda, const nvc_bf16* W, void* C,
                                           // first ring lap of W before the dependency wait + L2 prefetch ahead of the ring:
                                           // helps the short, latency-bound k-loops of decode (K <= 3072: 5.1 vs 5.7 us), costs
                                           // 2 - 8 % on the long ones (K 12288 at M 64: 23.2 -> 21.6 us without it) and at M >= 256
-                                          (g_nvc_gemm_prefetch && M <= BM && kb_total <= 48) ? 1 : 0,
-                                          ks, epi, ctx->gemm_ws, ctx->gemm_counters, trace));
+                                          (g_nvc_gemm_prefetch && M <= BM && kb_total <= 48 && !tile_group) ? 1 : 0,
+                                          ks, epi, ctx->gemm_ws, ctx->gemm_counters, trace, tile_group, N));
   NVC_CUDA_CHECK(ctx, cudaGetLastError());
   ctx->launches++;
   return NVC_OK;
@@ -531,7 +542,7 @@ static int gemm_impl(nvc_ctx* ctx, const nvc_bf16* A, int lda, const nvc_bf16* W
   NVC_REQUIRE(ctx, lda % 8 == 0 && lda >= K, NVC_ESHAPE, "lda must be >= K and a multiple of 8");
   NVC_REQUIRE(ctx, ldc >= (nvc_epi_gated(epi) ? Nout / 2 : Nout) && ldc % 8 == 0, NVC_ESHAPE,
               "ldc must be >= the output width and a multiple of 8");
-  NVC_REQUIRE(ctx, epi == NVC_EPI_NONE || (nvc_epi_gated(epi) && Nout % 32 == 0 && out_dtype == NVC_DT_BF16),
+  NVC_REQUIRE(ctx, epi == NVC_EPI_NONE || epi == NVC_EPI_RELU2 || (nvc_epi_gated(epi) && Nout % 32 == 0 && out_dtype == NVC_DT_BF16),
               NVC_ESHAPE, "fused SiLU-mul epilogue needs Nout % 32 == 0 and bf16 output");
   NVC_REQUIRE(ctx, out_dtype == NVC_DT_BF16 || out_dtype == NVC_DT_F32, NVC_EINVAL, "bad out_dtype");
   NVC_REQUIRE(ctx, ((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0 && ((uintptr_t)C % 16) == 0, NVC_EINVAL,
@@ -626,6 +637,42 @@ extern "C" int nvc_gemm_bf16_gelu_mul(nvc_ctx* ctx, const nvc_bf16* A, int lda, 
                                       int I, int K, void* stream) {
   NVC_REQUIRE(ctx, I > 0 && I % 16 == 0, NVC_ESHAPE, "I must be a multiple of 16");
   return gemm_impl(ctx, A, lda, W_gu16, act, ldc, NVC_DT_BF16, M, 2 * I, K, 0, 0, NVC_EPI_GELU_TANH_MUL, stream, nullptr);
+}
+
+// C = act(A W^T) with the plain activations of nvc_linear (NVC_ACT_NONE, NVC_ACT_RELU2) in the epilogue.
+extern "C" int nvc_gemm_bf16_act(nvc_ctx* ctx, const nvc_bf16* A, int lda, const nvc_bf16* W, void* C, int ldc, int out_dtype, int M,
+                                 int Nout, int K, int act, void* stream) {
+  NVC_REQUIRE(ctx, act == NVC_ACT_NONE || act == NVC_ACT_RELU2, NVC_EINVAL, "activation must be NVC_ACT_NONE or NVC_ACT_RELU2");
+  return gemm_impl(ctx, A, lda, W, C, ldc, out_dtype, M, Nout, K, 0, 0, act == NVC_ACT_RELU2 ? NVC_EPI_RELU2 : NVC_EPI_NONE, stream, nullptr);
+}
+
+// Grouped product on the 1-CTA kernel: rows of A sorted by group with every group starting at a multiple of 128 rows
+// (nvc_moe_sort_padded), W = [groups][Nout][K]; C[r] = act(A[r] . W[tile_group[r / 128]]^T).  M_cap is the host-known upper
+// bound of the padded row count (a multiple of 128); which tiles exist is decided on the device by tile_group, so the launch
+// needs no host round trip and replays inside a CUDA graph.
+extern "C" int nvc_gemm_bf16_grouped(nvc_ctx* ctx, const nvc_bf16* A, int lda, const nvc_bf16* W, void* C, int ldc, int out_dtype,
+                                     int M_cap, int Nout, int K, const int32_t* tile_group, int groups, int act, void* stream) {
+  NVC_REQUIRE(ctx, ctx && A && W && C && tile_group, NVC_EINVAL, "null pointer");
+  NVC_REQUIRE(ctx, M_cap >= 0 && M_cap % BM == 0 && Nout > 0 && K > 0 && groups > 0, NVC_EINVAL, "bad sizes (M_cap must be a multiple of 128)");
+  NVC_REQUIRE(ctx, K % 64 == 0 && Nout % 16 == 0, NVC_ESHAPE, "K must be a multiple of 64 and Nout of 16");
+  NVC_REQUIRE(ctx, lda % 8 == 0 && lda >= K && ldc % 8 == 0 && ldc >= Nout, NVC_ESHAPE, "row strides must cover the rows and be multiples of 8");
+  NVC_REQUIRE(ctx, out_dtype == NVC_DT_BF16 || out_dtype == NVC_DT_F32, NVC_EINVAL, "bad out_dtype");
+  NVC_REQUIRE(ctx, act == NVC_ACT_NONE || act == NVC_ACT_RELU2, NVC_EINVAL, "activation must be NVC_ACT_NONE or NVC_ACT_RELU2");
+  NVC_REQUIRE(ctx, ((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0 && ((uintptr_t)C % 16) == 0, NVC_EINVAL,
+              "pointers must be 16-byte aligned");
+  NVC_REQUIRE(ctx, ctx->encode_tiled != nullptr, NVC_EDEVICE, "cuTensorMapEncodeTiled unavailable");
+  if (M_cap == 0) return NVC_OK;
+  int bn, kps, splits, cl = 1, ks = 0;
+  choose_config(ctx, M_cap > BM ? M_cap : BM + 1, Nout, K, false, &bn, &kps, &splits, &cl, &ks);   // the many-tile choice: CL = 1, no split
+  const int epi = act == NVC_ACT_RELU2 ? NVC_EPI_RELU2 : NVC_EPI_NONE;
+  cudaStream_t st = nvc_stream(stream);
+  const int f32 = out_dtype == NVC_DT_F32;
+#define X(BN, KPS, CL) \
+  if (bn == BN && kps == KPS && CL == 1) return launch<BN, KPS, CL>(ctx, A, lda, W, C, ldc, f32, M_cap, Nout, K, 1, 0, epi, st, nullptr, tile_group, groups);
+  NVC_GEMM_CONFIGS(X)
+#undef X
+  NVC_REQUIRE(ctx, false, NVC_EINVAL, "unsupported tile configuration");
+  return NVC_OK;
 }
 
 extern "C" int nvc_gemm_bf16_silu_mul(nvc_ctx* ctx, const nvc_bf16* A, int lda, const nvc_bf16* W_gu16, nvc_bf16* act,

@@ -71,6 +71,7 @@ struct LayerW {
   void *w_eup = nullptr, *w_edown = nullptr;  // [E][effp, Wp], [E][Wp, effp]
   void *w_sup = nullptr, *w_sdown = nullptr;  // [sfp, Wp], [Wp, sfp]
   int qrp = 0, kvp = 0, dimp = 0, vdp = 0, ffp = 0, effp = 0, sfp = 0;
+  bool moe_tc = false;                        // experts through the grouped tcgen05 product (groups padded to 128 rows)
 };
 
 struct KaruzenBody : nvc_model_body {
@@ -80,6 +81,7 @@ struct KaruzenBody : nvc_model_body {
   size_t esz = 2;
   int Wp = 0, Vp = 0;
   bool use_tc = true;                  // tcgen05 GEMMs for the plain products of the bf16 mode
+  bool use_moe_tc = true;              // grouped tcgen05 products for the experts (bf16, padded expert size of 128 and more)
   bool use_flash = true;               // tcgen05 paged-prefill kernel for long prompt portions (bf16, padded latent of 128)
   std::vector<LayerW> L;
   std::vector<void*> cache;            // per run: [slots, kvp]
@@ -91,7 +93,8 @@ struct KaruzenBody : nvc_model_body {
   float *x0 = nullptr, *res = nullptr, *down = nullptr, *mix = nullptr, *ffo = nullptr, *y = nullptr, *sd = nullptr;
   void *h = nullptr, *cq = nullptr, *q = nullptr, *qabs = nullptr, *olat = nullptr, *ao = nullptr, *gu = nullptr, *act = nullptr,
        *hid = nullptr, *su = nullptr, *hn = nullptr;
-  int32_t *tk_idx = nullptr, *offsets = nullptr, *src_rows = nullptr, *pos = nullptr;
+  int32_t *tk_idx = nullptr, *offsets = nullptr, *src_rows = nullptr, *pos = nullptr, *tile_group = nullptr;
+  void* xs = nullptr;                  // rows of h gathered into the experts' padded groups
   float *tk_w = nullptr, *gate = nullptr, *zlog = nullptr;
   void* attn_ws = nullptr;             // key-split partials of small decode batches
   size_t attn_ws_bytes = 0;
@@ -171,6 +174,7 @@ struct KaruzenBody : nvc_model_body {
     esz = dt == NVC_DT_F32 ? 4 : 2;
     use_tc = dt == NVC_DT_BF16 && !(getenv("NVC_KARUZEN_TC") && atoi(getenv("NVC_KARUZEN_TC")) == 0);
     use_flash = use_tc && !(getenv("NVC_KARUZEN_FLASH") && atoi(getenv("NVC_KARUZEN_FLASH")) == 0);
+    use_moe_tc = use_tc && !(getenv("NVC_KARUZEN_MOE_TC") && atoi(getenv("NVC_KARUZEN_MOE_TC")) == 0);
     runs = cfg.runs();
     Wp = pad64(cfg.width);
     Vp = pad64(cfg.vocab);
@@ -179,6 +183,7 @@ struct KaruzenBody : nvc_model_body {
     int rc;
     L.resize(cfg.layers.size());
     size_t m_down = 0, m_cq = 0, m_q = 0, m_qabs = 0, m_ao = 0, m_gu = 0, m_act = 0, m_hid = 0, m_su = 0, m_top = 0, m_E = 0, m_Ep = 0;
+    size_t m_prow = 0, m_effp = 0, m_tcrow = 0;     // rows of the sorted (token, choice) layout, padded where the groups are
     int64_t wbytes = 0;
     for (size_t i = 0; i < cfg.layers.size(); ++i) {
       const auto& m = cfg.layers[i].mixer;
@@ -235,6 +240,12 @@ struct KaruzenBody : nvc_model_body {
           m_su = std::max(m_su, (size_t)w.sfp);
         }
         m_hid = std::max(m_hid, (size_t)f.top * w.effp);
+        // The tcgen05 tile is 128 rows: experts narrower than that (after padding) stay with the mma.sync product.
+        w.moe_tc = use_moe_tc && w.effp >= 128 && Wp >= 128;
+        const size_t rows = w.moe_tc ? moe_tiles((int)std::min<size_t>(T * f.top, 0x3fffffff), f.experts) * (size_t)128 : T * f.top;
+        m_prow = std::max(m_prow, rows);
+        if (w.moe_tc) m_tcrow = std::max(m_tcrow, rows);
+        m_effp = std::max(m_effp, (size_t)w.effp);
         m_top = std::max(m_top, (size_t)f.top);
         m_E = std::max(m_E, (size_t)f.experts);
       }
@@ -256,9 +267,10 @@ struct KaruzenBody : nvc_model_body {
     if (m_gu && ((rc = zalloc(r, &gu, T * m_gu * esz)) || (rc = zalloc(r, &act, T * m_act * esz)))) return rc;
     if (m_top) {
       if ((rc = zalloc(r, &tk_idx, T * m_top * 4)) || (rc = zalloc(r, &tk_w, T * m_top * 4)) || (rc = zalloc(r, &gate, T * 4)) || (rc = zalloc(r, &zlog, T * m_Ep * 4)) ||
-          (rc = zalloc(r, &offsets, (m_E + 1) * 4)) || (rc = zalloc(r, &src_rows, T * m_top * 4)) || (rc = zalloc(r, &pos, T * m_top * 4)) ||
-          (rc = zalloc(r, &hid, T * m_hid * esz)) || (rc = zalloc(r, &y, T * m_top * Wp * 4)))
+          (rc = zalloc(r, &offsets, (m_E + 1) * 4)) || (rc = zalloc(r, &src_rows, m_prow * 4)) || (rc = zalloc(r, &pos, T * m_top * 4)) ||
+          (rc = zalloc(r, &hid, m_prow * m_effp * esz)) || (rc = zalloc(r, &y, m_prow * Wp * 4)))
         return rc;
+      if (m_tcrow && ((rc = zalloc(r, &xs, m_tcrow * Wp * esz)) || (rc = zalloc(r, &tile_group, (m_tcrow / 128 + 1) * 4)))) return rc;
       if (m_su && ((rc = zalloc(r, &su, T * m_su * esz)) || (rc = zalloc(r, &sd, T * Wp * 4)))) return rc;
     }
     if ((rc = zalloc(r, &hn, (size_t)r->max_logit_rows * Wp * esz))) return rc;
@@ -400,6 +412,8 @@ struct KaruzenBody : nvc_model_body {
   // Prompt portions of this step go through the tcgen05 paged-prefill kernel when the storage is bf16, the padded latent is
   // that kernel's head size and the block size is one it tiles; shorter portions stay with the latent kernel (a 128-row
   // query tile per head would be mostly empty).
+  // 128-row tiles that P sorted pairs of E groups can take when every group is padded to a multiple of 128
+  static int moe_tiles(int P, int E) { return (int)(((int64_t)P + (int64_t)E * 127 + 127) / 128); }
   static constexpr int kFlashMinChunk = 64;
   bool flash_portions(const nvc_runner* r, const nvc_step_shape& s, int kvp) const {
     const int bs = r->opt.kvcache_block_size;
@@ -515,6 +529,24 @@ struct KaruzenBody : nvc_model_body {
                                        w.w_sup ? gate : nullptr, N, st)))
           return rc;
         mark(r, "moe_route");
+        if (w.moe_tc) {
+          // groups padded to the 128-row tile of the tcgen05 kernel; which tiles exist is a device table (no host round trip)
+          const int tiles = moe_tiles(P, f.experts), mcap = tiles * 128;
+          if ((rc = nvc_moe_sort_padded(ctx, tk_idx, N, f.top, f.experts, 128, offsets, src_rows, pos, tile_group, tiles, st))) return rc;
+          mark(r, "moe_sort");
+          if ((rc = nvc_gather_rows_bf16(ctx, reinterpret_cast<const nvc_bf16*>(h), Wp, src_rows, offsets + f.experts,
+                                         reinterpret_cast<nvc_bf16*>(xs), Wp, mcap, Wp, st)))
+            return rc;
+          mark(r, "moe_gather");
+          if ((rc = nvc_gemm_bf16_grouped(ctx, reinterpret_cast<const nvc_bf16*>(xs), Wp, reinterpret_cast<const nvc_bf16*>(w.w_eup), hid,
+                                          w.effp, NVC_DT_BF16, mcap, w.effp, Wp, tile_group, f.experts, NVC_ACT_RELU2, st)))
+            return rc;
+          mark(r, "moe_up");
+          if ((rc = nvc_gemm_bf16_grouped(ctx, reinterpret_cast<const nvc_bf16*>(hid), w.effp, reinterpret_cast<const nvc_bf16*>(w.w_edown), y,
+                                          Wp, NVC_DT_F32, mcap, Wp, w.effp, tile_group, f.experts, NVC_ACT_NONE, st)))
+            return rc;
+          mark(r, "moe_down");
+        } else {
         if ((rc = nvc_moe_sort(ctx, tk_idx, N, f.top, f.experts, offsets, src_rows, pos, st))) return rc;
         mark(r, "moe_sort");
         if ((rc = nvc_linear_grouped(ctx, h, Wp, src_rows, w.w_eup, Wp, (int64_t)w.effp * Wp, hid, w.effp, offsets, f.experts, P, dt, odt,
@@ -525,9 +557,16 @@ struct KaruzenBody : nvc_model_body {
                                      NVC_DT_F32, Wp, w.effp, NVC_ACT_NONE, st)))
           return rc;
         mark(r, "moe_down");
+        }
         if (w.w_sup) {
-          if ((rc = linear(r, h, Wp, w.w_sup, su, w.sfp, odt, N, w.sfp, Wp))) return rc;
-          if ((rc = nvc_act_mul(ctx, su, w.sfp, su, w.sfp, dt, N, f.shared_ff, w.sfp, NVC_ACT_RELU2, st))) return rc;
+          if (use_tc) {      // squared relu in the epilogue of the up-projection
+            if ((rc = nvc_gemm_bf16_act(ctx, reinterpret_cast<const nvc_bf16*>(h), Wp, reinterpret_cast<const nvc_bf16*>(w.w_sup), su, w.sfp,
+                                        NVC_DT_BF16, N, w.sfp, Wp, NVC_ACT_RELU2, st)))
+              return rc;
+          } else {
+            if ((rc = linear(r, h, Wp, w.w_sup, su, w.sfp, odt, N, w.sfp, Wp))) return rc;
+            if ((rc = nvc_act_mul(ctx, su, w.sfp, su, w.sfp, dt, N, f.shared_ff, w.sfp, NVC_ACT_RELU2, st))) return rc;
+          }
           if ((rc = linear(r, su, w.sfp, w.w_sdown, sd, Wp, NVC_DT_F32, N, Wp, w.sfp))) return rc;
           mark(r, "shared_expert");
         }

@@ -127,11 +127,12 @@ __global__ void moe_route_kernel(const T* __restrict__ h, int ldh, const float* 
 // expert's group, and the warp then places its pairs in order (__match_any_sync ranks equal experts inside a batch of
 // 32).  Within an expert the pairs keep token order, so the layout - and every sum downstream - is deterministic.
 __global__ void __launch_bounds__(1024)
-moe_sort_kernel(const int32_t* __restrict__ idx, int P, int top, int E, int32_t* __restrict__ offsets,
-                int32_t* __restrict__ src_rows, int32_t* __restrict__ pos) {
-  extern __shared__ int32_t sm[];   // [32][E] counts -> starts, then [E + 1] offsets
+moe_sort_kernel(const int32_t* __restrict__ idx, int P, int top, int E, int align, int32_t* __restrict__ offsets,
+                int32_t* __restrict__ src_rows, int32_t* __restrict__ pos, int32_t* __restrict__ tile_group, int tiles_cap) {
+  extern __shared__ int32_t sm[];   // [32][E] counts -> starts, then [E + 1] offsets, then [E] sizes
   int32_t* cnt = sm;
   int32_t* off = sm + 32 * E;
+  int32_t* size = off + E + 1;
   pdl_trigger();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -144,14 +145,24 @@ moe_sort_kernel(const int32_t* __restrict__ idx, int P, int top, int E, int32_t*
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     int total = 0;
     for (int w = 0; w < 32; ++w) total += cnt[w * E + e];
-    off[e + 1] = total;                                  // sizes for now
+    size[e] = total;
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
+  if (threadIdx.x == 0) {                                // every group starts at a multiple of `align` rows
     off[0] = 0;
-    for (int e = 0; e < E; ++e) off[e + 1] += off[e];
+    for (int e = 0; e < E; ++e) off[e + 1] = off[e] + (size[e] + align - 1) / align * align;
   }
   __syncthreads();
+  if (align > 1) {
+    // rows between a group's last pair and the next group's start have no source; tiles of `align` rows -> their group
+    for (int e = warp; e < E; e += blockDim.x >> 5) {
+      for (int r = off[e] + size[e] + lane; r < off[e + 1]; r += 32) src_rows[r] = -1;
+      if (tile_group)
+        for (int t = off[e] / align + lane; t < off[e + 1] / align; t += 32) tile_group[t] = e;
+    }
+    if (tile_group)
+      for (int t = off[E] / align + threadIdx.x; t < tiles_cap; t += blockDim.x) tile_group[t] = -1;
+  }
   for (int e = threadIdx.x; e < E; e += blockDim.x) {    // counts -> first position of (warp, expert)
     int a = off[e];
     for (int w = 0; w < 32; ++w) {
@@ -175,6 +186,21 @@ moe_sort_kernel(const int32_t* __restrict__ idx, int P, int top, int E, int32_t*
     __syncwarp();
     if (have && lane == 31 - __clz(peers)) cnt[warp * E + e] += __popc(peers);   // the last peer advances the group
     __syncwarp();
+  }
+}
+
+// out[r] = in[src_rows[r]] for r < *num_rows (a device count), zeros where src_rows[r] < 0; 16 bytes per thread
+__global__ void gather_rows_kernel(const uint4* __restrict__ in, int ld_in, const int32_t* __restrict__ src_rows,
+                                   const int32_t* __restrict__ num_rows, uint4* __restrict__ out, int ld_out, int rows_cap, int per_row,
+                                   int rows_per_cta) {
+  pdl_trigger();
+  pdl_wait();
+  const int n = min(rows_cap, *num_rows);
+  for (int i = threadIdx.x; i < rows_per_cta * per_row; i += blockDim.x) {
+    const int r = blockIdx.x * rows_per_cta + i / per_row, c = i % per_row;
+    if (r >= n) break;
+    const int src = src_rows[r];
+    out[(int64_t)r * ld_out + c] = src >= 0 ? in[(int64_t)src * ld_in + c] : make_uint4(0u, 0u, 0u, 0u);
   }
 }
 
@@ -229,10 +255,33 @@ int nvc_moe_route_logits(nvc_ctx* ctx, const float* z, int ldz, const float* cor
 
 int nvc_moe_sort(nvc_ctx* ctx, const int32_t* topk_idx, int N, int top, int E, int32_t* offsets, int32_t* src_rows, int32_t* pos,
                  void* stream) {
+  return nvc_moe_sort_padded(ctx, topk_idx, N, top, E, 1, offsets, src_rows, pos, nullptr, 0, stream);
+}
+
+int nvc_moe_sort_padded(nvc_ctx* ctx, const int32_t* topk_idx, int N, int top, int E, int align, int32_t* offsets, int32_t* src_rows,
+                        int32_t* pos, int32_t* tile_group, int tiles_cap, void* stream) {
   NVC_REQUIRE(ctx, ctx && topk_idx && offsets && src_rows && pos, NVC_EINVAL, "null pointer");
-  NVC_REQUIRE(ctx, N >= 0 && top > 0 && E > 0 && E <= 320, NVC_EINVAL, "bad sizes");
-  NVC_CUDA_CHECK(ctx, nvc_launch(ctx, moe_sort_kernel, dim3(1), dim3(1024), (size_t)(33 * E + 1) * sizeof(int32_t), nvc_stream(stream),
-                                 topk_idx, N * top, top, E, offsets, src_rows, pos));
+  NVC_REQUIRE(ctx, N >= 0 && top > 0 && E > 0 && E <= 320 && align >= 1, NVC_EINVAL, "bad sizes");
+  NVC_REQUIRE(ctx, !tile_group || (align > 1 && (int64_t)tiles_cap * align >= (int64_t)N * top + (int64_t)E * (align - 1)), NVC_EINVAL,
+              "tile_group needs align > 1 and room for every group's padding");
+  NVC_CUDA_CHECK(ctx, nvc_launch(ctx, moe_sort_kernel, dim3(1), dim3(1024), (size_t)(34 * E + 1) * sizeof(int32_t), nvc_stream(stream),
+                                 topk_idx, N * top, top, E, align, offsets, src_rows, pos, tile_group, tiles_cap));
+  ctx->launches++;
+  return NVC_OK;
+}
+
+int nvc_gather_rows_bf16(nvc_ctx* ctx, const nvc_bf16* in, int ld_in, const int32_t* src_rows, const int32_t* num_rows, nvc_bf16* out,
+                         int ld_out, int rows_cap, int width, void* stream) {
+  NVC_REQUIRE(ctx, ctx && in && src_rows && num_rows && out, NVC_EINVAL, "null pointer");
+  NVC_REQUIRE(ctx, rows_cap >= 0 && width > 0 && width % 8 == 0 && ld_in % 8 == 0 && ld_out % 8 == 0 && ld_in >= width && ld_out >= width,
+              NVC_ESHAPE, "width and row strides must be multiples of 8");
+  NVC_REQUIRE(ctx, ((uintptr_t)in % 16) == 0 && ((uintptr_t)out % 16) == 0, NVC_EINVAL, "pointers must be 16-byte aligned");
+  if (rows_cap == 0) return NVC_OK;
+  const int per_row = width / 8;                                   // 16-byte chunks per row
+  const int rows_per_cta = std::max(1, 256 / per_row);
+  NVC_CUDA_CHECK(ctx, nvc_launch(ctx, gather_rows_kernel, dim3((rows_cap + rows_per_cta - 1) / rows_per_cta), dim3(256), 0, nvc_stream(stream),
+                                 reinterpret_cast<const uint4*>(in), ld_in / 8, src_rows, num_rows, reinterpret_cast<uint4*>(out), ld_out / 8,
+                                 rows_cap, per_row, rows_per_cta));
   ctx->launches++;
   return NVC_OK;
 }

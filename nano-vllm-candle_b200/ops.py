@@ -414,6 +414,46 @@ def moe_sort(ctx, idx: torch.Tensor, E: int):
     return offsets, src, pos
 
 
+def moe_sort_padded(ctx, idx: torch.Tensor, E: int, align: int = 128):
+    """Groups padded to multiples of `align` rows: (offsets [E + 1], src [tiles * align] with -1 in the padding, pos, tile_group)."""
+    N, top = idx.shape
+    tiles = (N * top + E * (align - 1) + align - 1) // align
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=idx.device)
+    src = torch.full((tiles * align,), -7, dtype=torch.int32, device=idx.device)
+    pos = torch.empty(N * top, dtype=torch.int32, device=idx.device)
+    tile_group = torch.full((tiles,), -7, dtype=torch.int32, device=idx.device)
+    check(ctx.l.nvc_moe_sort_padded(ctx.h, _ptr(idx), N, top, E, align, _ptr(offsets), _ptr(src), _ptr(pos), _ptr(tile_group), tiles,
+                                    _stream()), "nvc_moe_sort_padded", ctx.h)
+    return offsets, src, pos, tile_group
+
+
+def gather_rows(ctx, x: torch.Tensor, src: torch.Tensor, num_rows: torch.Tensor) -> torch.Tensor:
+    """out[r] = x[src[r]] for r < num_rows[0] (zeros where src[r] < 0); rows behind num_rows keep the fill value."""
+    out = torch.full((src.numel(), x.shape[1]), 3.0, dtype=x.dtype, device=x.device)
+    check(ctx.l.nvc_gather_rows_bf16(ctx.h, _ptr(x), x.stride(0), _ptr(src), _ptr(num_rows), _ptr(out), out.stride(0), src.numel(),
+                                     x.shape[1], _stream()), "nvc_gather_rows_bf16", ctx.h)
+    return out
+
+
+def gemm_act(ctx, A, W, act: int = ACT_NONE, out_dtype=None) -> torch.Tensor:
+    """act(A W^T) on the tcgen05 kernels, the activation in the epilogue."""
+    M, K = A.shape
+    N = W.shape[0]
+    C_ = torch.empty(M, N, dtype=out_dtype or A.dtype, device=A.device)
+    check(ctx.l.nvc_gemm_bf16_act(ctx.h, _ptr(A), A.stride(0), _ptr(W), _ptr(C_), N, _dt(C_), M, N, K, act, _stream()),
+          "nvc_gemm_bf16_act", ctx.h)
+    return C_
+
+
+def gemm_grouped(ctx, A, W, tile_group, act: int = ACT_NONE, out_dtype=None) -> torch.Tensor:
+    """A [tiles * 128, K] sorted by group (groups padded to 128 rows), W [groups, N, K]: act(A[r] . W[tile_group[r // 128]]^T)."""
+    G, N, K = W.shape
+    C_ = torch.zeros(A.shape[0], N, dtype=out_dtype or A.dtype, device=A.device)
+    check(ctx.l.nvc_gemm_bf16_grouped(ctx.h, _ptr(A), A.stride(0), _ptr(W), _ptr(C_), N, _dt(C_), A.shape[0], N, K, _ptr(tile_group), G, act,
+                                      _stream()), "nvc_gemm_bf16_grouped", ctx.h)
+    return C_
+
+
 def moe_combine(ctx, y, pos, w, shared=None, gate=None) -> torch.Tensor:
     N, top = w.shape
     H = y.shape[1]

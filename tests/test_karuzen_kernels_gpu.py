@@ -155,6 +155,62 @@ def test_linear_grouped_with_empty_and_ragged_groups(ctx, ops, dt):
     assert torch.allclose(out.float().cpu(), want, **tol(dt))
 
 
+@pytest.mark.parametrize("E,top,N", [(6, 2, 700), (16, 3, 45), (1, 1, 130), (70, 8, 33), (5, 5, 128), (9, 1, 1)])
+def test_padded_sort_gather_and_grouped_tensor_core_product(ctx, ops, E, top, N):
+    """Groups padded to the 128-row tile: offsets, padding rows, positions and the tile table of the sort; the gather; the
+    grouped tcgen05 product (squared relu in the epilogue, fp32 and bf16 outputs) against a loop over the experts.  Expert
+    choices are skewed so that some experts get nothing and one gets several tiles."""
+    g = torch.Generator().manual_seed(100 + E + N)
+    Kd, F = 192, 80
+    score = torch.randn(N, E, generator=g) + torch.linspace(2.0, -2.0, E)
+    if E > 2:
+        score[:, 1] = -1e9                                        # an expert that nobody chooses
+    idx = score.topk(top, dim=-1).indices.to(torch.int32)
+    offsets, src, pos, tile_group = ops.moe_sort_padded(ctx, idx.to(DEV), E)
+    offsets, src, pos, tile_group = offsets.cpu().long(), src.cpu().long(), pos.cpu().long(), tile_group.cpu().long()
+    counts = torch.bincount(idx.flatten().long(), minlength=E)
+    starts = torch.zeros(E + 1, dtype=torch.long)
+    starts[1:] = ((counts + 127) // 128 * 128).cumsum(0)
+    assert torch.equal(offsets, starts)
+    used = int(starts[-1]) // 128
+    for e in range(E):
+        lo, n = int(starts[e]), int(counts[e])
+        pairs = (idx.flatten().long() == e).nonzero().flatten()  # in token order: the sort is stable
+        assert torch.equal(src[lo:lo + n], pairs // top)
+        assert torch.equal(pos[pairs], torch.arange(lo, lo + n))
+        assert (src[lo + n:int(starts[e + 1])] == -1).all()
+        assert (tile_group[lo // 128:int(starts[e + 1]) // 128] == e).all()
+    assert (tile_group[used:] == -1).all() and tile_group.numel() >= used
+    x = torch.randn(N, Kd, generator=g).bfloat16()
+    xs = ops.gather_rows(ctx, x.to(DEV), src.to(torch.int32).to(DEV), offsets[-1:].to(torch.int32).to(DEV))
+    live = src[:used * 128]
+    want_xs = torch.where((live >= 0).unsqueeze(1), x.float()[live.clamp(min=0)], torch.zeros(1))
+    assert torch.equal(xs[:used * 128].float().cpu(), want_xs)
+    assert (xs[used * 128:] == 3.0).all()                        # rows behind the device count are not touched
+    W = (torch.randn(E, F, Kd, generator=g) * 0.1).bfloat16()
+    for act, odt in ((ops.ACT_RELU2, torch.bfloat16), (ops.ACT_NONE, torch.float32)):
+        out = ops.gemm_grouped(ctx, xs, W.to(DEV), tile_group.to(torch.int32).to(DEV), act=act, out_dtype=odt).float().cpu()
+        for e in range(E):
+            lo, n = int(starts[e]), int(counts[e])
+            ref = want_xs[lo:lo + n] @ W[e].float().T
+            if act == ops.ACT_RELU2:
+                ref = torch.relu(ref) ** 2
+            assert torch.allclose(out[lo:lo + n], ref, **(tol(odt) if odt == torch.bfloat16 else dict(rtol=1e-4, atol=1e-4))), f"expert {e}"
+        assert (out[used * 128:] == 0).all()                     # tiles behind the last group are skipped
+
+
+@pytest.mark.parametrize("M", [1, 77, 128, 300, 1100])
+def test_squared_relu_in_the_product_epilogue(ctx, ops, M):
+    g = torch.Generator().manual_seed(M)
+    A, W = torch.randn(M, 128, generator=g).bfloat16(), (torch.randn(208, 128, generator=g) * 0.2).bfloat16()
+    want = torch.relu(A.float() @ W.float().T) ** 2
+    for odt in (torch.bfloat16, torch.float32):
+        out = ops.gemm_act(ctx, A.to(DEV), W.to(DEV), ops.ACT_RELU2, odt)
+        assert torch.allclose(out.float().cpu(), want, **(tol(odt) if odt == torch.bfloat16 else dict(rtol=1e-4, atol=1e-4)))
+    plain = ops.gemm_act(ctx, A.to(DEV), W.to(DEV), ops.ACT_NONE, torch.float32)
+    assert torch.allclose(plain.cpu(), A.float() @ W.float().T, rtol=1e-4, atol=1e-4)
+
+
 @pytest.mark.parametrize("E,top", [(6, 2), (16, 3), (1, 1), (70, 8), (5, 5)])
 def test_moe_route_sort_combine(ctx, ops, E, top):
     g = torch.Generator().manual_seed(8 + E)

@@ -201,6 +201,26 @@ def cfg_c():
     ], loop={"start": 0, "stop": 2, "times": 2})
 
 
+def cfg_d():
+    """Experts wide enough (128 and more after padding) for the grouped tcgen05 products of the bf16 mode; every expert is
+    chosen, so that no rounding of a router's input can flip a choice."""
+    return K.make_config(vocab=200, width=192, layers=[
+        {"type": "latent_attention", "mixer": K.mixer_cfg(2, 32, 32, 64, 32, 0.2), "mlp": K.moe_cfg(3, 3, 136, 1.2, 72)},
+        {"type": "latent_attention", "mixer": K.mixer_cfg(3, 16, 16, 48, 24, 0.25), "mlp": K.moe_cfg(2, 2, 200, 0.8, 0)},
+    ], loop=None)
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_wide_experts(dtype):
+    r = Rig(cfg_d(), dtype, blocks=40, seed=21)
+    try:
+        V = r.cfg["vocab"]
+        pr = {"a": toks(300, V, 70), "b": toks(45, V, 71), "c": toks(2, V, 72)}
+        r.check(pr, [[("a", 200), ("b", 1)], [("b", 1), ("a", 99), ("c", 2)], [("a", 1), ("b", 43)]])
+    finally:
+        r.close()
+
+
 @pytest.mark.parametrize("flash", ["1", "0"])
 def test_long_portions_beside_decoded_tokens(monkeypatch, flash):
     """Portions of 64 tokens and more - whole prompts, behind a cached prefix that ends inside a page, beside one-token
