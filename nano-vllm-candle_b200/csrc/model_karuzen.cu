@@ -524,7 +524,12 @@ struct KaruzenBody : nvc_model_body {
       } else if (f.kind == nvc_karuzen_mlp::Moe) {
         const int P = N * f.top;
         // router logits (and the shared gate's, one more row) as one product with fp32 accumulation and output
-        if ((rc = nvc_linear(ctx, h, Wp, 0, w.router, Wp, 0, zlog, w.Ep, 0, dt, NVC_DT_F32, N, f.experts + 1, Wp, 1, NVC_ACT_NONE, st))) return rc;
+        // (all Ep padded columns on the tcgen05 kernel - the padding rows of the matrix are zero - or the logical ones on the FMA kernel)
+        if (use_tc) {
+          if ((rc = linear(r, h, Wp, w.router, zlog, w.Ep, NVC_DT_F32, N, w.Ep, Wp))) return rc;
+        } else if ((rc = nvc_linear(ctx, h, Wp, 0, w.router, Wp, 0, zlog, w.Ep, 0, dt, NVC_DT_F32, N, f.experts + 1, Wp, 1, NVC_ACT_NONE, st))) {
+          return rc;
+        }
         if ((rc = nvc_moe_route_logits(ctx, zlog, w.Ep, w.corr, f.experts, f.top, f.router_scale, w.w_sup ? f.experts : -1, tk_idx, tk_w,
                                        w.w_sup ? gate : nullptr, N, st)))
           return rc;

@@ -219,6 +219,29 @@ __global__ void moe_combine_kernel(const TY* __restrict__ y, int ldy, const int3
   }
 }
 
+// the same sum on fp32 rows whose width and strides are multiples of 4: 16-byte loads and stores, same order of additions
+__global__ void moe_combine_f4_kernel(const float4* __restrict__ y, int ldy4, const int32_t* __restrict__ pos, const float* __restrict__ w,
+                                      int top, const float4* __restrict__ shared, int lds4, const float* __restrict__ gate,
+                                      float4* __restrict__ out, int ldo4, int H4) {
+  pdl_trigger();
+  pdl_wait();
+  const int n = blockIdx.x;
+  const float g = shared ? (gate ? gate[n] : 1.0f) : 0.f;
+  for (int j = threadIdx.x; j < H4; j += blockDim.x) {
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int t = 0; t < top; ++t) {
+      const float wt = w[(int64_t)n * top + t];
+      const float4 v = y[(int64_t)pos[(int64_t)n * top + t] * ldy4 + j];
+      a.x = fmaf(wt, v.x, a.x); a.y = fmaf(wt, v.y, a.y); a.z = fmaf(wt, v.z, a.z); a.w = fmaf(wt, v.w, a.w);
+    }
+    if (shared) {
+      const float4 v = shared[(int64_t)n * lds4 + j];
+      a.x += v.x * g; a.y += v.y * g; a.z += v.z * g; a.w += v.w * g;
+    }
+    out[(int64_t)n * ldo4 + j] = a;
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -292,6 +315,14 @@ int nvc_moe_combine(nvc_ctx* ctx, const void* y, int y_dtype, int ldy, const int
   NVC_REQUIRE(ctx, ctx && y && pos && topk_w && out, NVC_EINVAL, "null pointer");
   NVC_REQUIRE(ctx, N >= 0 && H > 0 && top > 0 && ldy >= H && ldo >= H && (!shared || lds >= H), NVC_EINVAL, "bad sizes");
   if (N == 0) return NVC_OK;
+  if (y_dtype == NVC_DT_F32 && (!shared || shared_dtype == NVC_DT_F32) && H % 4 == 0 && ldy % 4 == 0 && ldo % 4 == 0 &&
+      (!shared || lds % 4 == 0) && ((uintptr_t)y % 16) == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)shared % 16) == 0) {
+    NVC_CUDA_CHECK(ctx, nvc_launch(ctx, moe_combine_f4_kernel, dim3(N), dim3(H / 4 >= 256 ? 256 : (H / 4 > 32 ? 128 : 32)), 0, nvc_stream(stream),
+                                   reinterpret_cast<const float4*>(y), ldy / 4, pos, topk_w, top, reinterpret_cast<const float4*>(shared), lds / 4,
+                                   gate, reinterpret_cast<float4*>(out), ldo / 4, H / 4));
+    ctx->launches++;
+    return NVC_OK;
+  }
   const dim3 grid(N), block(H >= 1024 ? 512 : 128);
 #define NVC_COMBINE(TY, TS)                                                                                                        \
   NVC_CUDA_CHECK(ctx, nvc_launch(ctx, moe_combine_kernel<TY, TS>, grid, block, 0, nvc_stream(stream), reinterpret_cast<const TY*>(y), \

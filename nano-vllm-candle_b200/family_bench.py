@@ -145,7 +145,7 @@ def karuzen_rooflines(cfg, prof: Dict[str, float], N: int, B: int, ctx_lens: Lis
                 out[name] = _roof(L * 2.0 * N * top * ef * W, L * 2.0 * (touched * ef * W + N * top * (ef + W)), prof[name], pk)
         if "shared_expert" in prof:
             out["shared_expert"] = _roof(L * 4.0 * N * sf * W, L * 2.0 * (2 * sf * W + N * (2 * sf + 2 * W)), prof["shared_expert"], pk)
-    for name in ("dyt_norm", "latent_norm_store", "gelu_mul", "moe_route", "moe_sort", "moe_combine", "embed", "final_norm", "lm_head"):
+    for name in ("dyt_norm", "latent_norm_store", "gelu_mul", "moe_route", "moe_sort", "moe_gather", "moe_combine", "embed", "final_norm", "lm_head"):
         if name in prof:
             out[name] = {"us": round(prof[name], 2)}
     return out
