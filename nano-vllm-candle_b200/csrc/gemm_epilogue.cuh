@@ -34,14 +34,12 @@ __device__ __forceinline__ void nvc_gated16(int epi, const float* f, float* o) {
     }
   }
 }
-// the element-wise epilogues on 32 accumulator columns: squared relu, or a copy (a select per element keeps both arrays in
-// registers; choosing between two array pointers would not)
-__device__ __forceinline__ void nvc_unary32(int epi, const float* f, float* o) {
-  const bool r2 = epi == NVC_EPI_RELU2;
+// squared relu of 32 accumulator columns
+__device__ __forceinline__ void nvc_relu2_32(const float* f, float* o) {
 #pragma unroll
   for (int j = 0; j < 32; ++j) {
     const float r = fmaxf(f[j], 0.f);
-    o[j] = r2 ? r * r : f[j];
+    o[j] = r * r;
   }
 }
 #endif
@@ -77,6 +75,8 @@ __device__ __forceinline__ void store16(void* C, int out_f32, int64_t off, const
 //                    rows [16g,16g+16)), so f[0..16) = gate and f[16..32) = up of features n0/2 .. n0/2+16:
 //                    C[row, n0/2 .. n0/2+16) = silu(gate) * up   (src/layers/activation.rs:13-18,
 //                    silu(x) = x / (1 + exp(-x)) in f32), bf16.  row_off = row * ldc in elements of C.
+// kUnary = false compiles the element-wise epilogues (NVC_EPI_RELU2) out: the decode GEMMs of the dense models keep their code.
+template <bool kUnary = true>
 __device__ __forceinline__ void emit32(void* C, int out_f32, int epi, int64_t row_off, int n0, int N, const float* f) {
   if (nvc_epi_gated(epi)) {
     if (n0 < N) {
@@ -87,10 +87,15 @@ __device__ __forceinline__ void emit32(void* C, int out_f32, int epi, int64_t ro
       store16(C, 0, row_off + (n0 >> 1), o);
     }
   } else {
-    float g[32];
-    nvc_unary32(epi, f, g);
-    if (n0 < N) store16(C, out_f32, row_off + n0, g);
-    if (n0 + 16 < N) store16(C, out_f32, row_off + n0 + 16, g + 16);
+    if (kUnary && epi == NVC_EPI_RELU2) {          // a branch of its own, uniform over the grid
+      float g[32];
+      nvc_relu2_32(f, g);
+      if (n0 < N) store16(C, out_f32, row_off + n0, g);
+      if (n0 + 16 < N) store16(C, out_f32, row_off + n0 + 16, g + 16);
+      return;
+    }
+    if (n0 < N) store16(C, out_f32, row_off + n0, f);
+    if (n0 + 16 < N) store16(C, out_f32, row_off + n0 + 16, f + 16);
   }
 }
 
@@ -141,17 +146,24 @@ struct RowStage {
       if (filled == 128) flush(lane);
       return;
     }
-    float g[32];
-    nvc_unary32(epi, f, g);
-    if (out_f32) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) put(lane, make_uint4(__float_as_uint(g[4 * j]), __float_as_uint(g[4 * j + 1]),
-                                                       __float_as_uint(g[4 * j + 2]), __float_as_uint(g[4 * j + 3])));
+    if (epi == NVC_EPI_RELU2) {          // a branch of its own (uniform over the grid): the plain path pays nothing for it
+      float g[32];
+      nvc_relu2_32(f, g);
+      put32(lane, out_f32, g);
     } else {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) put(lane, pack8(g + 8 * j));
+      put32(lane, out_f32, f);
     }
     if (filled == 128) flush(lane);
+  }
+  __device__ __forceinline__ void put32(int lane, int out_f32, const float* f) {
+    if (out_f32) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) put(lane, make_uint4(__float_as_uint(f[4 * j]), __float_as_uint(f[4 * j + 1]),
+                                                       __float_as_uint(f[4 * j + 2]), __float_as_uint(f[4 * j + 3])));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) put(lane, pack8(f + 8 * j));
+    }
   }
   __device__ __forceinline__ void finish(int lane) {
     if (filled) flush(lane);

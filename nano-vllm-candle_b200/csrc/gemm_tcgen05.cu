@@ -56,7 +56,8 @@ __device__ __forceinline__ int atomic_add_acq_rel_gpu(int* p, int v) {
   return old;
 }
 
-template <int BN, int KPS, int CL>
+// kExt: the variant with the grouped mode (tile_group) and the element-wise epilogues; the plain variant compiles both out
+template <int BN, int KPS, int CL, bool kExt = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                          void* __restrict__ C, int ldc, int out_f32, int M, int N, int k_blocks_total,
@@ -145,9 +146,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   // m-tile t multiplies with the weight rows of group tile_group[t] ([group][N][K] in W).  The table is written by an
   // earlier kernel of the stream, so it is read after the wait (past L1).  A negative entry marks a tile behind the last
   // group: its CTA computes nothing and only tears down.
-  const int grp = tile_group ? __ldcg(tile_group + m_tile) : 0;
-  const bool skip = grp < 0;
-  const int w_row0 = n_tile * BN + (tile_group ? grp * group_w_rows : 0);
+  int grp = 0;
+  if constexpr (kExt) grp = tile_group ? __ldcg(tile_group + m_tile) : 0;
+  const bool skip = kExt && grp < 0;
+  const int w_row0 = n_tile * BN + grp * (kExt ? group_w_rows : 0);
 
   if (skip) {
     // nothing to load or multiply
@@ -246,7 +248,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
           float f[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-          if (row_ok) emit32(C, out_f32, epi, (int64_t)grow * ldc, n_tile * BN + c * 16, N, f);
+          if (row_ok) emit32<kExt>(C, out_f32, epi, (int64_t)grow * ldc, n_tile * BN + c * 16, N, f);
         }
       } else {
         uint32_t v[16];
@@ -433,7 +435,13 @@ int launch(nvc_ctx* ctx, const nvc_bf16* A, int lda, const nvc_bf16* W, void* C,
   // ks_cluster: the eff_splits CTAs of one output tile form a cluster (1,1,S) and reduce over DSMEM
   const int ks = (ks_cluster && CL == 1 && eff_splits > 1 && eff_splits <= 8) ? 1 : 0;
   NVC_REQUIRE(ctx, !ks || (size_t)BN * BM * 4 <= (size_t)cfg::kStages * cfg::kStageBytes, NVC_EINVAL, "ring too small for the partial tile");
-  NVC_CUDA_CHECK(ctx, nvc_launch_cluster3(ctx, gemm_bf16_tcgen05_kernel<BN, KPS, CL>, grid, dim3(kThreads), cfg::kSmemBytes,
+  // the extended variant exists for CL = 1 (the grouped products and the element-wise epilogues never use clusters)
+  constexpr bool kHasExt = CL == 1;
+  const bool ext = tile_group != nullptr || epi == NVC_EPI_RELU2;
+  NVC_REQUIRE(ctx, !ext || kHasExt, NVC_EINVAL, "grouped / element-wise epilogue products need a cluster size of 1");
+  auto kernel = gemm_bf16_tcgen05_kernel<BN, KPS, CL, false>;
+  if constexpr (kHasExt) { if (ext) kernel = gemm_bf16_tcgen05_kernel<BN, KPS, CL, true>; }
+  NVC_CUDA_CHECK(ctx, nvc_launch_cluster3(ctx, kernel, grid, dim3(kThreads), cfg::kSmemBytes,
                                           stream, dim3(CL, 1, ks ? eff_splits : 1), ta, tb, C, ldc, out_f32, M, N, kb_total,
                                           kb_per, a_rows / CL,
                                           // first ring lap of W before the dependency wait + L2 prefetch ahead of the ring:
@@ -524,9 +532,12 @@ void choose_config(const nvc_ctx* ctx, int M, int N, int K, bool allow_split, in
 }  // namespace
 
 extern "C" int nvc_gemm_init(nvc_ctx* ctx) {
-#define X(BN, KPS, CL)                                                               \
-  NVC_CUDA_CHECK(ctx, cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, KPS, CL>,    \
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN, KPS>::kSmemBytes));
+#define X(BN, KPS, CL)                                                                                                   \
+  NVC_CUDA_CHECK(ctx, cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, KPS, CL, false>,                                 \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN, KPS>::kSmemBytes));      \
+  if (CL == 1)                                                                                                           \
+    NVC_CUDA_CHECK(ctx, cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, KPS, 1, true>,                                 \
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN, KPS>::kSmemBytes));
   NVC_GEMM_CONFIGS(X)
 #undef X
   return NVC_OK;
@@ -588,6 +599,7 @@ static int gemm_impl(nvc_ctx* ctx, const nvc_bf16* A, int lda, const nvc_bf16* W
     splits = 1;
     ks = 0;
     if (bn < 32) { bn = 32; kps = 4; cl = 1; }
+    if (epi == NVC_EPI_RELU2) cl = 1;          // (every (bn, kps) the choice returns has a CL = 1 instantiation)
   }
   if (splits > K / BK) splits = K / BK;
   const int tiles = ((M + BM - 1) / BM) * ((Nout + bn - 1) / bn);
