@@ -1,10 +1,11 @@
 // Latent attention on the tensor pipe (bf16 storage): 16 query rows - any (token, head) pairs of ONE sequence, each with
 // its own causal bound - are the M dimension of mma.sync.m16n8k16, the shared latent row of a token is both the key (read
 // with ldmatrix) and the value (the SAME shared-memory tile read with ldmatrix.trans), so one 16-token tile is loaded
-// once for S = Q C^T and O += P C.  CTA = 4 warps on one 16-row chunk; warp w owns the 16-token tiles w, w + 4, ...
-// of the keys the chunk can see (private 3-stage cp.async ring, 16-byte-chunk XOR swizzle), online softmax in the log2
-// domain on the accumulator fragments, fp32 accumulators; the warps meet once, in the final merge.  Decode rows
-// (q_len = 1: `heads` rows per sequence) and prompt portions (q_len * heads rows) are the same code.
+// once for S = Q C^T and O += P C.  Online softmax in the log2 domain on the accumulator fragments, fp32 accumulators.
+// Fewer than 64 rows (decode, q_len = 1: `heads` rows per sequence; short portions): the CTA's 4 warps work on one 16-row chunk, warp w owns the
+// 16-token tiles w, w + 4, ... of the keys (private 3-stage cp.async ring, 16-byte-chunk XOR swizzle) and the warps meet once,
+// in the final merge.  Many rows (a prompt portion, q_len * heads >= 64): the CTA takes 64 consecutive rows, 16 per warp,
+// and all warps read the same 64-token tiles from one ring of the CTA.  Both in one launch, chosen per sequence.
 // DP = padded latent width (64 or 128 numbers per row; padding columns of q and of the cache rows are zero).
 #pragma once
 #include "paged_decode_mma.cuh"
