@@ -373,6 +373,73 @@ int nvc_latent_attn_paged(nvc_ctx* ctx, const void* q, int ldq, const void* cach
                           int D, int head_stride, int block_size, float scale, void* out, int ldo, int dtype, void* workspace,
                           size_t workspace_bytes, void* stream);
 
+/* ---- mechanisms of the models with RMS norms on an fp32 residual stream, windowed / sink attention and retention (Ranilix) ---- */
+/* out[n, :H] = f32(table[ids[n], :H]) * scale. */
+int nvc_embed_gather_scaled_f32(nvc_ctx* ctx, const int32_t* ids, const void* table, int table_dtype, int ldt, float scale, float* out,
+                                int ldo, int N, int H, void* stream);
+/* RMS norms fused with the residual accumulation (all sums fp32), up to two norms of the same sum:
+ *   s = res_in[r] + a0[r] + a1[r]   (each operand optional, fp32 [*, ld]);  res_out[r] = s (optional, may alias);
+ *   out0[i, :H] = s / sqrt(mean(s^2) + eps) * w0,  out1[i, :H] = ... * w1   (w0 == NULL: accumulate only; w1 optional).
+ * rows == NULL: r = i; else r = rows[i] (gathers N rows; res_out must be NULL).  Both outputs have the row stride ldo. */
+int nvc_rms_norm_pair(nvc_ctx* ctx, const float* res_in, const float* a0, const float* a1, float* res_out, int ld, const float* w0,
+                      void* out0, const float* w1, void* out1, int out_dtype, int ldo, float eps, const int32_t* rows, int N, int H,
+                      void* stream);
+/* Output stage of a mixer, per (row, head) of vdim numbers: y = o (norm == 0) or o / sqrt(mean(o^2) + eps) (norm != 0, no
+ * weight); out = y * act(gate) * out_scale with act = sigmoid or z sigmoid(z); gate == NULL: no gate.  o, gate: fp32. */
+enum { NVC_GATE_SIGMOID = 0, NVC_GATE_SILU = 1 };
+int nvc_head_gate(nvc_ctx* ctx, const float* o, int ldo, const float* gate, int ldg, void* out, int ldout, int out_dtype, int heads,
+                  int vdim, int norm, float eps, int act, float out_scale, int N, void* stream);
+/* (cos, sin) of position * base^(-2 i / dims), i < dims / 2, for positions below max_pos: out fp32 [max_pos, dims / 2, 2] in
+ * device memory, angles taken in double precision on the host.  Synchronous. */
+int nvc_rotary_table_init_sync(nvc_ctx* ctx, float base, int dims, int max_pos, float* out);
+/* Everything between a fused q / k / v projection (fp32 rows `in`) and the attention or recurrence behind it, in one pass:
+ * bias; per-head RMS norm of q and k (weights of `dim` numbers shared by the heads); rotary positions on the first rot_dims
+ * numbers of every q / k head - pairs (2i, 2i + 1), or (i, i + rot_dims / 2) when rot_half - with (cos, sin) from rot_table at
+ * positions[n]; k *= k_scale; value blending (NVC_BLEND_PROVIDE: v_first[n] = v, NVC_BLEND_MIX: v <- (1 - *lambda) v +
+ * *lambda v_first[n]); q goes to q_out[n], k and v to row slot_mapping[n] of k_out / v_out (a paged cache; a negative slot
+ * skips the token) or to row n when slot_mapping == NULL. */
+enum { NVC_BLEND_NONE = 0, NVC_BLEND_PROVIDE = 1, NVC_BLEND_MIX = 2 };
+typedef struct nvc_qkv_prep {
+  const float* in; int ldi;
+  const float* bias;                      /* indexed like a row of `in`; NULL: none */
+  int q_off, k_off, v_off;                /* first column of q / k / v in a row */
+  int q_heads, kv_heads, dim, vdim;
+  const float* q_norm; const float* k_norm; float eps;   /* both or neither */
+  int rot_dims, rot_half; const float* rot_table; const int32_t* positions;
+  float k_scale;
+  int blend; const float* lambda; float* v_first; int ldvf;
+  void* q_out; int ldq;
+  void* k_out; void* v_out; int ldk, ldv;
+  const int32_t* slot_mapping;
+  int q_dtype, kv_dtype;
+} nvc_qkv_prep;
+int nvc_qkv_prep_run(nvc_ctx* ctx, const nvc_qkv_prep* p, int N, void* stream);
+/* Grouped-query softmax attention over a paged cache with separate key and value widths:
+ *   out[i, h, :vdim] = out_scale * gate_i,h * sum_j p_j v_j,   p_j = exp(s_j) / (sum_j' exp(s_j') + exp(sink_h)),
+ *   s_j = scale * q[i, h] . k[j, h / (heads / kv_heads)],  j over max(0, pos_i - window + 1) .. pos_i  (window == 0: from 0).
+ * sink (fp32 [heads]) and gate (fp32 [rows, ldg], through a sigmoid) are optional.  Rows, block tables and context lengths
+ * as in nvc_latent_attn_paged (cu_seqlens == NULL: one row per sequence); rows = total query rows, max_qlen the longest
+ * portion.  dim, vdim <= 512.  bf16 storage with dim and vdim multiples of 16 up to 256 runs on the tensor pipe, everything
+ * else on the FMA pipe. */
+typedef struct nvc_attn_spec {
+  int heads, kv_heads, dim, vdim;
+  float scale;
+  int window;
+  const float* sink;
+  const float* gate; int ldg;
+  float out_scale;
+} nvc_attn_spec;
+int nvc_attn_paged_wide(nvc_ctx* ctx, const void* q, int ldq, const void* k_cache, int ldk, const void* v_cache, int ldv,
+                        const int32_t* block_tables, int bt_stride, const int32_t* context_lens, const int32_t* cu_seqlens, int B,
+                        int rows, int max_qlen, int block_size, const nvc_attn_spec* spec, void* out, int ldo, int dtype, void* stream);
+/* Retention: S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t per head over the new tokens of every sequence (rows
+ * cu_seqlens[b] .. cu_seqlens[b + 1], or row b when cu_seqlens == NULL).  state: fp32 [slots, heads, dim, vdim]; sequence b
+ * uses slot state_slots[b], starts from zeros when positions[first row] == 0 and leaves its last state in the slot.
+ * q, k, v, o: fp32 rows. */
+int nvc_retention_scan(nvc_ctx* ctx, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, float* o, int ldo,
+                       float* state, const int32_t* state_slots, const int32_t* cu_seqlens, const int32_t* positions,
+                       const float* decay, int B, int heads, int dim, int vdim, void* stream);
+
 /* K8. Replaces Qwen3ModelRunner::argmax (src/engine/llm_engine.rs:135-142) on device:
  * idx[b] = LAST index of the maximum of logits[b, :] (Iterator::max_by tie rule);
  * val[b] = that maximum.  idx is offset by `index_offset` (TP vocab shard). */

@@ -70,8 +70,10 @@ int nvc_runner_finalize(nvc_runner* r);
 
 /* ---- model registry: any registered architecture from its config.json ----
  * The architecture is config.json's "architecture" (or the first of HF's "architectures"): "Qwen3ForCausalLM" (the
- * built-in body above) or "Karuzen" (parallel layers with a Dynamic-Tanh norm, latent attention, dense or
- * mixture-of-experts feed-forward, a looped block of layers; fp32 residual stream).  Error text:
+ * built-in body above), "Karuzen" (parallel layers with a Dynamic-Tanh norm, latent attention, dense or
+ * mixture-of-experts feed-forward, a looped block of layers; fp32 residual stream) or "Ranilix" (parallel layers with two
+ * RMS norms; windowed attention with a sink, value blending and an output gate, or causal attention beside retention with a
+ * per-sequence recurrent state; squared-relu feed-forward; fp32 residual stream).  Error text:
  * nvc_model_config_last_error (thread-local). */
 typedef struct nvc_model_config nvc_model_config;
 const char* nvc_model_config_last_error(void);
@@ -95,6 +97,13 @@ int nvc_runner_takes_raw_tensors(const nvc_runner* r);
 /* 1 when every step of the runner attends through the paged cache (the engine then never calls nvc_runner_prefill). */
 int nvc_runner_needs_block_tables(const nvc_runner* r);
 int nvc_runner_vocab(const nvc_runner* r);
+/* Models with per-sequence recurrent state (Ranilix's retention) keep it in max_num_seqs state slots beside the paged cache:
+ * nvc_runner_num_state_slots > 0, and before EVERY step the caller names the slot of each sequence of that step, in batch
+ * order (distinct, in [0, slots)).  A sequence whose first token of a step sits at position 0 starts from an empty state;
+ * any other continues from what its slot holds, so a slot belongs to one sequence from its first token to its last and a
+ * cached prefix can not be skipped.  nvc_engine does this by itself (state slots are taken and given back with the blocks). */
+int nvc_runner_num_state_slots(const nvc_runner* r);
+int nvc_runner_set_state_slots(nvc_runner* r, const int32_t* slots, int B);
 /* Arms the NEXT prefill / mixed step to compute logits for `n` given rows of its flat token list (instead of the last
  * row of every sequence); nvc_runner_last_logits then returns [n, vocab].  Such a step samples nothing (out_tokens = -1).
  * n <= max_logit_rows.  rows == NULL disarms. */

@@ -70,6 +70,8 @@ def declare(l: C.CDLL) -> None:
         "nvc_runner_needs_block_tables": [_vp],
         "nvc_runner_vocab": [_vp],
         "nvc_runner_set_logit_rows": [_vp, _vp, _i],
+        "nvc_runner_num_state_slots": [_vp],
+        "nvc_runner_set_state_slots": [_vp, _vp, _i],
         "nvc_runner_set_residual_tap": [_vp, _vp, _i64],
         "nvc_runner_layer_runs": [_vp],
         "nvc_runner_arm_profile": [_vp],

@@ -40,6 +40,7 @@ struct Sequence {
   double temperature = 1.0;
   size_t max_tokens = 64;
   bool ignore_eos = false;
+  int32_t state_slot = -1;          // models with recurrent state: the slot that holds this sequence's state while it has blocks
 
   size_t len() const { return num_tokens; }
   bool is_finished() const { return status == Status::Finished; }
@@ -121,6 +122,26 @@ struct BlockManager {
   FreeList free_;
   std::unordered_map<uint64_t, int32_t> hash_to_block;
   int64_t cache_hits = 0, cache_queries = 0;   // in blocks
+  // State slots of models with per-sequence recurrent state (0: the model has none).  A sequence takes one with its first
+  // blocks and gives it back with them (finish, preemption, close), so a slot's content always belongs to the sequence that
+  // holds it; a re-admitted sequence starts again at position 0, where the runner resets the state.
+  int num_state_slots = 0;
+  std::deque<int32_t> free_state;
+  void init_state_slots(int n) {
+    num_state_slots = n;
+    free_state.clear();
+    for (int i = 0; i < n; ++i) free_state.push_back(i);
+  }
+  bool state_available(const Sequence& s) const { return num_state_slots == 0 || s.state_slot >= 0 || !free_state.empty(); }
+  void take_state(Sequence& s) {
+    if (num_state_slots == 0 || s.state_slot >= 0) return;
+    s.state_slot = free_state.front();
+    free_state.pop_front();
+  }
+  void release_state(Sequence& s) {
+    if (s.state_slot >= 0) free_state.push_back(s.state_slot);
+    s.state_slot = -1;
+  }
 
   BlockManager(int num_blocks, int block_size, bool prefix)
       : num_blocks_(num_blocks), block_size_(block_size), prefix_caching(prefix), blocks(num_blocks), free_(num_blocks) {
@@ -146,8 +167,9 @@ struct BlockManager {
     hash_to_block[h] = id;
   }
 
-  bool can_allocate(const Sequence& s) const { return free_.size() >= s.num_blocks(); }
+  bool can_allocate(const Sequence& s) const { return free_.size() >= s.num_blocks() && state_available(s); }
   void allocate(Sequence& s) {
+    take_state(s);
     s.block_table.clear();
     s.num_cached_tokens = 0;
     const size_t bs = (size_t)block_size_, nb = s.num_blocks();
@@ -196,6 +218,7 @@ struct BlockManager {
     }
     s.block_table.clear();
     s.num_cached_tokens = 0;
+    release_state(s);
   }
   // A step that failed in the runner never wrote the K / V of its sequences: their blocks must not
   // serve prefix-cache hits.  (A block shared with a sequence outside the batch only loses its cache entry.)
@@ -214,6 +237,7 @@ struct BlockManager {
   // Caller-driven sequences (nvc_engine_step_forced) grow by whole portions: blocks up to `nb` in total.
   size_t blocks_missing(const Sequence& s, size_t nb) const { return nb > s.block_table.size() ? nb - s.block_table.size() : 0; }
   void grow(Sequence& s, size_t nb) {
+    take_state(s);
     while (s.block_table.size() < nb) {
       const int32_t id = free_.front();
       take(id);
@@ -554,6 +578,14 @@ int arm_sampling(nvc_engine* e) {
   return nvc_runner_set_sampling(e->runner, e->temps.data(), e->streams.data(), (int)e->batch.size(), e->sampling_seed);
 }
 
+// models with recurrent state: tell the runner which state slot every sequence of the batch owns
+int arm_state_slots(nvc_engine* e) {
+  if (!e->runner || e->scheduler.block_manager.num_state_slots == 0) return NVC_OK;
+  std::vector<int32_t> slots;
+  for (auto& s : e->batch) slots.push_back(s->state_slot);
+  return nvc_runner_set_state_slots(e->runner, slots.data(), (int)slots.size());
+}
+
 void rollback_failed_step(nvc_engine* e) {
   auto& run = e->scheduler.running;
   for (auto it = e->batch.rbegin(); it != e->batch.rend(); ++it) {   // reverse: preempt() pushes to the FRONT of waiting
@@ -611,9 +643,12 @@ int nvc_engine_create(const nvc_scheduler_config* cfg, nvc_runner* runner, nvc_e
     c.max_num_batched_tokens = std::min(c.max_num_batched_tokens, ro.max_num_batched_tokens);
     c.max_model_len = c.max_model_len == 0 ? ro.max_model_len : std::min(c.max_model_len, ro.max_model_len);
     if (c.enable_chunked_prefill && c.max_num_batched_tokens < c.max_num_seqs) return NVC_EINVAL;
+    // recurrent state is built token by token: a sequence can not skip a cached prefix
+    if (nvc_runner_num_state_slots(runner) > 0 && c.enable_prefix_caching) return NVC_EINVAL;
   }
   *out = new nvc_engine(c, runner);
   (*out)->scheduler.max_model_len = (size_t)c.max_model_len;
+  if (runner != nullptr) (*out)->scheduler.block_manager.init_state_slots(nvc_runner_num_state_slots(runner));
   return NVC_OK;
 }
 
@@ -706,6 +741,9 @@ int nvc_engine_step(nvc_engine* e, nvc_step_output* out) {
     for (int i = 0; i < B; ++i) e->out_tokens[i] = e->batch[i]->last_token + 1;   // DummyModelRunner
   } else if (e->sampling && (rc = arm_sampling(e)) != NVC_OK) {
     e->err = "nvc_runner_set_sampling failed";
+    return rc;
+  } else if ((rc = arm_state_slots(e)) != NVC_OK) {
+    e->err = "nvc_runner_set_state_slots failed";
     return rc;
   } else if (e->chunked && e->num_decode == B) {
     // nothing but one-token sequences: the decode step proper (captured CUDA graph, fused peer all-reduce)
@@ -829,6 +867,14 @@ int nvc_engine_step_forced(nvc_engine* e, int n, const int64_t* seq_ids, const i
     e->err = "step_forced: KV pool exhausted";
     return NVC_ENOMEM;
   }
+  if (bm.num_state_slots > 0) {
+    size_t need = 0;
+    for (auto& p : seqs) need += p->state_slot < 0 ? 1 : 0;
+    if (need > bm.free_state.size()) {
+      e->err = "step_forced: no free state slot";
+      return NVC_ENOMEM;
+    }
+  }
   // append the portions, grow the block tables; one-token continuations lead the batch (paged decode kernels)
   std::vector<int> order;
   {
@@ -885,6 +931,7 @@ int nvc_engine_step_forced(nvc_engine* e, int n, const int64_t* seq_ids, const i
   e->out_tokens.assign(B, 0);
   int rc = NVC_OK;
   if (!rows.empty()) rc = nvc_runner_set_logit_rows(e->runner, rows.data(), (int)rows.size());
+  if (rc == NVC_OK) rc = arm_state_slots(e);
   if (rc == NVC_OK) {
     if (rows.empty() && e->num_decode == B)
       rc = nvc_runner_decode(e->runner, e->ids.data(), e->positions.data(), e->slot_mapping.data(), e->block_tables.data(),

@@ -98,6 +98,96 @@ int parse_karuzen(const JValue& root, nvc_karuzen_config& c) {
   return NVC_OK;
 }
 
+bool parse_rotary(const JValue* m, nvc_rotary_spec& r, int dim, std::string& err) {
+  const JValue* rot = m->get("rot");
+  if (!rot || rot->kind == JValue::Null) { r.dims = 0; return true; }
+  if (rot->kind != JValue::Obj || !get_int(rot, "dims", r.dims, 0, err) || !get_float(rot, "base", r.base, err)) {
+    if (err.empty()) err = "`rot` must be an object";
+    return false;
+  }
+  if (r.dims % 2 != 0 || r.dims > dim) { err = "rot.dims must be even and at most dim"; return false; }
+  if (!(r.base > 0.f)) { err = "rot.base must be positive"; return false; }
+  return true;
+}
+
+bool parse_softmax_attn(const JValue* m, nvc_softmax_attn_spec& a, std::string& err) {
+  if (!get_int(m, "heads", a.heads, 1, err) || !get_int(m, "kv_heads", a.kv_heads, 1, err) || !get_int(m, "dim", a.dim, 1, err) ||
+      !get_int(m, "vdim", a.vdim, 1, err) || !get_float(m, "scale", a.scale, err) || !parse_rotary(m, a.rot, a.dim, err))
+    return false;
+  if (a.heads % a.kv_heads != 0) { err = "heads must be a multiple of kv_heads"; return false; }
+  return true;
+}
+
+int parse_ranilix(const JValue& root, nvc_ranilix_config& c) {
+  std::string err;
+  if (!get_int(&root, "vocab", c.vocab, 1, err) || !get_int(&root, "width", c.width, 1, err)) return cfg_fail(err);
+  const JValue* norm = root.get("norm");
+  if (!norm || norm->kind != JValue::Obj || !get_float(norm, "eps", c.eps, err)) return cfg_fail("norm.eps: " + err);
+  const JValue* emb = root.get("embedding");
+  c.embedding_scale = 1.f;
+  if (emb && emb->kind == JValue::Obj && emb->get("scale") && !get_float(emb, "scale", c.embedding_scale, err))
+    return cfg_fail("embedding.scale: " + err);
+  const JValue* layers = root.get("layers");
+  if (!layers || layers->kind != JValue::Arr || layers->arr.empty()) return cfg_fail("`layers` must be a non-empty list");
+  int blend_width = -1;
+  for (size_t i = 0; i < layers->arr.size(); ++i) {
+    const JValue& jl = layers->arr[i];
+    const std::string where = "layers[" + std::to_string(i) + "]: ";
+    if (jl.kind != JValue::Obj) return cfg_fail(where + "not an object");
+    nvc_ranilix_layer L;
+    const JValue* type = jl.get("type");
+    const JValue* m = jl.get("mixer");
+    if (!type || type->kind != JValue::Str) return cfg_fail(where + "missing `type`");
+    if (!m || m->kind != JValue::Obj) return cfg_fail(where + "missing `mixer`");
+    if (type->str == "attention") {
+      L.kind = nvc_ranilix_layer::Attention;
+      if (!parse_softmax_attn(m, L.attn, err)) return cfg_fail(where + "mixer: " + err);
+      const JValue* mask = m->get("mask");
+      if (mask && mask->kind == JValue::Obj) {
+        if (!get_int(mask, "size", L.attn.window, 1, err)) return cfg_fail(where + "mixer.mask: " + err);
+      } else if (mask && mask->kind != JValue::Null) {
+        return cfg_fail(where + "mixer.mask must be an object or null");
+      }
+      const JValue* vm = m->get("v_mix");
+      if (vm && vm->kind == JValue::Bool) L.attn.blend_values = vm->b;
+      else if (vm && vm->kind != JValue::Null) return cfg_fail(where + "mixer.v_mix must be true or false");
+      if (L.attn.blend_values) {
+        const int wv = L.attn.kv_heads * L.attn.vdim;
+        if (blend_width >= 0 && wv != blend_width) return cfg_fail(where + "layers that blend values must have equal kv_heads * vdim");
+        blend_width = wv;
+      }
+    } else if (type->str == "parallel") {
+      L.kind = nvc_ranilix_layer::Parallel;
+      const JValue* left = m->get("left");
+      const JValue* right = m->get("right");
+      if (!left || left->kind != JValue::Obj || !right || right->kind != JValue::Obj) return cfg_fail(where + "mixer needs `left` and `right`");
+      if (!parse_softmax_attn(left, L.attn, err)) return cfg_fail(where + "mixer.left: " + err);
+      if (!get_int(right, "heads", L.ret.heads, 1, err) || !get_int(right, "dim", L.ret.dim, 1, err) ||
+          !get_int(right, "vdim", L.ret.vdim, 1, err) || !parse_rotary(right, L.ret.rot, L.ret.dim, err))
+        return cfg_fail(where + "mixer.right: " + err);
+      const JValue* dec = right->get("decay");
+      if (!dec || dec->kind != JValue::Arr || (int)dec->arr.size() != L.ret.heads) return cfg_fail(where + "mixer.right.decay must list one number per head");
+      for (auto& d : dec->arr) {
+        if (d.kind != JValue::Num) return cfg_fail(where + "mixer.right.decay must list numbers");
+        L.ret.decay.push_back((float)d.num);
+      }
+      if (!get_float(m, "left_scale", L.left_scale, err) || !get_float(m, "right_scale", L.right_scale, err)) return cfg_fail(where + "mixer: " + err);
+    } else {
+      return cfg_fail(where + "mixer type `" + type->str + "` is not supported");
+    }
+    const JValue* mlp = jl.get("mlp");
+    if (mlp && mlp->kind == JValue::Obj) {
+      const JValue* kind = mlp->get("kind");
+      if (!kind || kind->kind != JValue::Str || kind->str != "dense") return cfg_fail(where + "mlp: only kind `dense` is supported");
+      if (!get_int(mlp, "ff", L.ff, 1, err)) return cfg_fail(where + "mlp: " + err);
+    } else if (mlp && mlp->kind != JValue::Null) {
+      return cfg_fail(where + "`mlp` must be an object or null");
+    }
+    c.layers.push_back(L);
+  }
+  return NVC_OK;
+}
+
 }  // namespace
 
 std::vector<nvc_karuzen_config::Run> nvc_karuzen_config::runs() const {
@@ -131,10 +221,12 @@ int nvc_model_config_from_json(const char* text, nvc_model_config** out) {
   int rc = NVC_OK;
   if (arch == "Karuzen") {
     rc = parse_karuzen(root, c->karuzen);
+  } else if (arch == "Ranilix") {
+    rc = parse_ranilix(root, c->ranilix);
   } else if (arch == "Qwen3ForCausalLM") {
     // parsed by nvc_qwen3_config_from_hf_dir (hf_loader.cpp) when loaded from a directory
   } else {
-    rc = cfg_fail("architecture `" + arch + "` is not registered (known: Qwen3ForCausalLM, Karuzen)");
+    rc = cfg_fail("architecture `" + arch + "` is not registered (known: Qwen3ForCausalLM, Karuzen, Ranilix)");
   }
   if (rc) { delete c; return rc; }
   *out = c;
@@ -158,9 +250,19 @@ void nvc_model_config_free(nvc_model_config* c) { delete c; }
 const char* nvc_model_config_architecture(const nvc_model_config* c) { return c ? c->architecture.c_str() : ""; }
 int nvc_model_config_vocab(const nvc_model_config* c) {
   if (!c) return 0;
+  if (c->architecture == "Ranilix") return c->ranilix.vocab;
   return c->architecture == "Karuzen" ? c->karuzen.vocab : c->qwen3.vocab_size;
 }
 int nvc_model_config_layer_runs(const nvc_model_config* c, int32_t* layers, int32_t* passes, int32_t* readd, int capacity) {
+  if (c && c->architecture == "Ranilix") {      // no looped block: every layer runs once
+    const int n = (int)c->ranilix.layers.size();
+    for (int i = 0; i < n && i < capacity; ++i) {
+      if (layers) layers[i] = i;
+      if (passes) passes[i] = 0;
+      if (readd) readd[i] = 0;
+    }
+    return n;
+  }
   if (!c || c->architecture != "Karuzen") return NVC_EINVAL;
   const auto runs = c->karuzen.runs();
   for (int i = 0; i < (int)runs.size() && i < capacity; ++i) {

@@ -34,9 +34,55 @@ struct nvc_karuzen_config {
   std::vector<Run> runs() const;
 };
 
+// Ranilix: a stack of parallel layers with two RMS norms of the same fp32 residual stream (one feeds the mixer, one the
+// squared-relu feed-forward).  Two kinds of mixer: "attention" (grouped-query attention with biases, per-head q / k norms,
+// partial interleaved rotary, a sliding window, a sink term in the softmax denominator, values blended with those of the
+// first blending layer, a sigmoid output gate) and "parallel" (plain causal grouped-query attention beside retention - a
+// per-head recurrent state with a fixed decay - summed with two constant weights).
+struct nvc_rotary_spec {
+  int dims = 0;              // leading numbers of a head that are rotated (0: none)
+  float base = 10000.f;
+};
+struct nvc_softmax_attn_spec {     // grouped-query softmax attention
+  int heads = 0, kv_heads = 0, dim = 0, vdim = 0;
+  float scale = 0.f;
+  nvc_rotary_spec rot;       // interleaved pairs (2i, 2i + 1)
+  int window = 0;            // 0: every earlier token is visible; n: the token itself and the n - 1 before it
+  bool blend_values = false; // v <- (1 - lambda) v + lambda v_first
+};
+struct nvc_retention_spec {
+  int heads = 0, dim = 0, vdim = 0;
+  nvc_rotary_spec rot;       // rotate-half pairs (i, i + dims / 2)
+  std::vector<float> decay;  // per head
+};
+struct nvc_ranilix_layer {
+  enum Kind { Attention, Parallel } kind = Attention;
+  nvc_softmax_attn_spec attn;      // the "attention" mixer, or the left half of "parallel"
+  nvc_retention_spec ret;          // the right half of "parallel"
+  float left_scale = 1.f, right_scale = 1.f;
+  int ff = 0;                      // 0: no feed-forward
+};
+struct nvc_ranilix_config {
+  int vocab = 0, width = 0;
+  float eps = 1e-5f;
+  float embedding_scale = 1.f;
+  std::vector<nvc_ranilix_layer> layers;
+  int first_blend_layer() const {
+    for (size_t i = 0; i < layers.size(); ++i)
+      if (layers[i].kind == nvc_ranilix_layer::Attention && layers[i].attn.blend_values) return (int)i;
+    return -1;
+  }
+  bool has_state() const {
+    for (auto& l : layers)
+      if (l.kind == nvc_ranilix_layer::Parallel) return true;
+    return false;
+  }
+};
+
 struct nvc_model_config {
-  std::string architecture;   // "Qwen3ForCausalLM" or "Karuzen"
+  std::string architecture;   // "Qwen3ForCausalLM", "Karuzen" or "Ranilix"
   nvc_qwen3_config qwen3{};
   int qwen3_tied = 0;
   nvc_karuzen_config karuzen;
+  nvc_ranilix_config ranilix;
 };

@@ -20,37 +20,11 @@
 #include <string>
 #include <vector>
 
+#include "body_common.h"
 #include "model_config.h"
 #include "runner.h"
 
 namespace {
-
-inline int pad64(int v) { return (v + 63) / 64 * 64; }
-
-inline float bf16_bits_to_f32(uint16_t h) {
-  uint32_t u = (uint32_t)h << 16;
-  float f;
-  memcpy(&f, &u, 4);
-  return f;
-}
-inline uint16_t f32_to_bf16_bits(float f) {
-  uint32_t u;
-  memcpy(&u, &f, 4);
-  if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x0040u);
-  return (uint16_t)((u + 0x7fffu + ((u >> 16) & 1u)) >> 16);
-}
-inline float f16_bits_to_f32(uint16_t h) {
-  const uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
-  uint32_t exp = (h >> 10) & 0x1fu, man = h & 0x3ffu, u;
-  if (exp == 0) {
-    if (man == 0) { u = sign; }
-    else { int e = -1; do { ++e; man <<= 1; } while (!(man & 0x400u)); u = sign | ((uint32_t)(127 - 15 - e) << 23) | ((man & 0x3ffu) << 13); }
-  } else if (exp == 31) { u = sign | 0x7f800000u | (man << 13); }
-  else { u = sign | ((exp + 112u) << 23) | (man << 13); }
-  float f;
-  memcpy(&f, &u, 4);
-  return f;
-}
 
 struct LayerW {
   // norm
@@ -74,13 +48,10 @@ struct LayerW {
   bool moe_tc = false;                        // experts through the grouped tcgen05 product (groups padded to 128 rows)
 };
 
-struct KaruzenBody : nvc_model_body {
+struct KaruzenBody : nvc_body_base {
   nvc_karuzen_config cfg;
   std::vector<nvc_karuzen_config::Run> runs;
-  int dt = NVC_DT_BF16;
-  size_t esz = 2;
   int Wp = 0, Vp = 0;
-  bool use_tc = true;                  // tcgen05 GEMMs for the plain products of the bf16 mode
   bool use_moe_tc = true;              // grouped tcgen05 products for the experts (bf16, padded expert size of 128 and more)
   bool use_flash = true;               // tcgen05 paged-prefill kernel for long prompt portions (bf16, padded latent of 128)
   std::vector<LayerW> L;
@@ -100,40 +71,7 @@ struct KaruzenBody : nvc_model_body {
   size_t attn_ws_bytes = 0;
   float* tap_host = nullptr;
   size_t tap_cap = 0;
-  bool prof_armed = false, prof_on = false;
-  std::vector<std::pair<const char*, cudaEvent_t>> marks;
-  std::string prof_json = "{}";
 
-  int arm_profile() override { prof_armed = true; return NVC_OK; }
-  bool profile_armed() const override { return prof_armed; }
-  const char* profile_json() const override { return prof_json.c_str(); }
-  // names the op(s) launched since the previous mark
-  void mark(nvc_runner* r, const char* name) {
-    if (!prof_on) return;
-    cudaEvent_t e;
-    if (cudaEventCreate(&e) != cudaSuccess) return;
-    cudaEventRecord(e, r->stream);
-    marks.emplace_back(name, e);
-  }
-  void finish_profile(nvc_runner* r) {
-    if (!prof_on) return;
-    prof_on = false;
-    cudaStreamSynchronize(r->stream);
-    std::map<std::string, double> us;
-    std::vector<std::string> order;
-    for (size_t i = 1; i < marks.size(); ++i) {
-      float ms = 0.f;
-      cudaEventElapsedTime(&ms, marks[i - 1].second, marks[i].second);
-      if (!us.count(marks[i].first)) order.push_back(marks[i].first);
-      us[marks[i].first] += ms * 1e3;
-    }
-    for (auto& m : marks) cudaEventDestroy(m.second);
-    marks.clear();
-    prof_json = "{";
-    for (size_t i = 0; i < order.size(); ++i)
-      prof_json += (i ? ", \"" : "\"") + order[i] + "\": " + std::to_string(us[order[i]]);
-    prof_json += "}";
-  }
 
   int vocab() const override { return cfg.vocab; }
   int logits_ld() const override { return Vp; }
@@ -150,23 +88,6 @@ struct KaruzenBody : nvc_model_body {
     return NVC_OK;
   }
 
-  template <typename P>
-  int zalloc(nvc_runner* r, P** p, size_t bytes) {
-    uint8_t* q = nullptr;
-    int rc = dev_alloc_bytes(r, &q, bytes);
-    if (rc) return rc;
-    *p = reinterpret_cast<P*>(q);
-    return NVC_OK;
-  }
-  int dev_alloc_bytes(nvc_runner* r, uint8_t** p, size_t bytes) {
-    void* q = nullptr;
-    bytes = std::max<size_t>(bytes, 256);
-    NVC_CUDA_CHECK(r->ctx, cudaMalloc(&q, bytes));
-    r->allocs.push_back(q);
-    NVC_CUDA_CHECK(r->ctx, cudaMemset(q, 0, bytes));
-    *p = reinterpret_cast<uint8_t*>(q);
-    return NVC_OK;
-  }
 
   int init(nvc_runner* r) {
     nvc_ctx* ctx = r->ctx;
@@ -283,25 +204,6 @@ struct KaruzenBody : nvc_model_body {
     return NVC_OK;
   }
 
-  // dst[(r0 + i) * ld + c0 + j] = src[i * scols + j] converted to the storage format (dst: device, T)
-  int put_matrix(nvc_runner* r, void* dst, size_t ld, size_t r0, size_t c0, const float* src, size_t rows, size_t cols, size_t src_rs,
-                 size_t src_cs) {
-    std::vector<uint8_t> stage(rows * cols * esz);
-    for (size_t i = 0; i < rows; ++i)
-      for (size_t j = 0; j < cols; ++j) {
-        const float v = src[i * src_rs + j * src_cs];
-        if (dt == NVC_DT_F32) memcpy(&stage[(i * cols + j) * 4], &v, 4);
-        else { const uint16_t b = f32_to_bf16_bits(v); memcpy(&stage[(i * cols + j) * 2], &b, 2); }
-      }
-    NVC_CUDA_CHECK(r->ctx, cudaMemcpy2D(reinterpret_cast<uint8_t*>(dst) + (r0 * ld + c0) * esz, ld * esz, stage.data(), cols * esz,
-                                        cols * esz, rows, cudaMemcpyHostToDevice));
-    return NVC_OK;
-  }
-  int put_f32(nvc_runner* r, float* dst, const float* src, size_t n) {
-    NVC_CUDA_CHECK(r->ctx, cudaMemcpy(dst, src, n * 4, cudaMemcpyHostToDevice));
-    return NVC_OK;
-  }
-
   int load_tensor(nvc_runner* r, const char* cname, const void* data, int st_dtype, const int64_t* shape, int ndim) override {
     nvc_ctx* ctx = r->ctx;
     const std::string name(cname);
@@ -309,11 +211,8 @@ struct KaruzenBody : nvc_model_body {
     if (it == want.end()) return NVC_OK;    // not a tensor of this configuration: ignored
     size_t n = 1;
     for (int i = 0; i < ndim; ++i) n *= (size_t)shape[i];
-    std::vector<float> v(n);
-    if (st_dtype == NVC_ST_F32) memcpy(v.data(), data, n * 4);
-    else if (st_dtype == NVC_ST_BF16) { const uint16_t* s = reinterpret_cast<const uint16_t*>(data); for (size_t i = 0; i < n; ++i) { uint16_t b; memcpy(&b, s + i, 2); v[i] = bf16_bits_to_f32(b); } }
-    else if (st_dtype == NVC_ST_F16) { const uint16_t* s = reinterpret_cast<const uint16_t*>(data); for (size_t i = 0; i < n; ++i) { uint16_t b; memcpy(&b, s + i, 2); v[i] = f16_bits_to_f32(b); } }
-    else NVC_REQUIRE(ctx, false, NVC_EINVAL, "unsupported dtype for " + name);
+    std::vector<float> v;
+    NVC_REQUIRE(ctx, tensor_to_f32(data, st_dtype, n, v), NVC_EINVAL, "unsupported dtype for " + name);
     const int64_t d0 = ndim > 0 ? shape[0] : 1, d1 = ndim > 1 ? shape[1] : 1;
     auto shape_is = [&](int64_t a, int64_t b) { return (ndim <= 2) && d0 == a && d1 == b && (ndim == 2 || b == 1); };
     auto bad = [&]() {
@@ -399,14 +298,6 @@ struct KaruzenBody : nvc_model_body {
       if (!kv.second && ++n <= 4) missing += kv.first + " ";
     NVC_REQUIRE(r->ctx, n == 0, NVC_ESTATE, "missing " + std::to_string(n) + " tensors: " + missing);
     return NVC_OK;
-  }
-
-  // C = A . W^T on padded shapes: the tcgen05 GEMM when it takes the shape, the FMA kernel otherwise
-  int linear(nvc_runner* r, const void* A, int lda, const void* Wt, void* C, int ldc, int out_dt, int M, int N, int K, int act = NVC_ACT_NONE) {
-    if (use_tc && act == NVC_ACT_NONE && K % 64 == 0 && N % 16 == 0 && lda % 8 == 0 && ldc % 8 == 0)
-      return nvc_gemm_bf16(r->ctx, reinterpret_cast<const nvc_bf16*>(A), lda, reinterpret_cast<const nvc_bf16*>(Wt), C, ldc, out_dt, M, N, K,
-                           r->stream);
-    return nvc_linear(r->ctx, A, lda, 0, Wt, K, 0, C, ldc, 0, dt, dt == NVC_DT_F32 ? NVC_DT_F32 : out_dt, M, N, K, 1, act, r->stream);
   }
 
   // Prompt portions of this step go through the tcgen05 paged-prefill kernel when the storage is bf16, the padded latent is

@@ -1,0 +1,134 @@
+// nvc_qkv_prep: everything between the fused q / k / v projection of a mixer and its attention or recurrence, in one pass
+// over the fp32 projection rows:
+//   + bias                                   (optional)
+//   per-head RMS norm of q and k             (optional; one weight vector of `dim` numbers shared by the heads)
+//   rotary positions on the first rot_dims numbers of every q / k head, pairs (2i, 2i + 1) or (i, i + rot_dims / 2),
+//                                            angles from a table of (cos, sin) per position
+//   k *= k_scale                             (after the rotation)
+//   value blending                           v <- (1 - lambda) v + lambda v_first, or v_first <- v in the layer that provides it
+//   stores                                   q to its buffer; k and v to rows of a paged cache (slot mapping) or to plain rows
+// One warp per (token, head) of q, k or v; a head is staged in shared memory so that any pairing reads its partner.
+#include "typed.cuh"
+
+namespace {
+
+struct PrepArgs {
+  nvc_qkv_prep p;
+  int N;
+};
+
+template <typename TQ, typename TKV>
+__global__ void qkv_prep_kernel(const PrepArgs a) {
+  extern __shared__ float stage[];
+  pdl_trigger();
+  pdl_wait();
+  const nvc_qkv_prep& p = a.p;
+  const int warps = blockDim.x >> 5, wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int units = p.q_heads + 2 * p.kv_heads;
+  const int64_t u = (int64_t)blockIdx.x * warps + wid;
+  if (u >= (int64_t)a.N * units) return;
+  const int n = (int)(u / units), uu = (int)(u % units);
+  const int wmax = p.dim > p.vdim ? p.dim : p.vdim;
+  float* x = stage + (size_t)wid * wmax;
+  const float* in = p.in + (int64_t)n * p.ldi;
+  if (uu >= p.q_heads + p.kv_heads) {
+    // ---- a value head
+    const int h = uu - p.q_heads - p.kv_heads;
+    const int col = p.v_off + h * p.vdim;
+    const int64_t orow = p.slot_mapping ? p.slot_mapping[n] : n;
+    const float lam = p.blend == NVC_BLEND_MIX ? __ldg(p.lambda) : 0.f;
+    for (int j = lane; j < p.vdim; j += 32) {
+      float v = in[col + j] + (p.bias ? __ldg(p.bias + col + j) : 0.f);
+      if (p.blend == NVC_BLEND_PROVIDE) p.v_first[(int64_t)n * p.ldvf + h * p.vdim + j] = v;
+      else if (p.blend == NVC_BLEND_MIX) v = (1.0f - lam) * v + lam * p.v_first[(int64_t)n * p.ldvf + h * p.vdim + j];
+      if (orow >= 0) st_f(reinterpret_cast<TKV*>(p.v_out) + orow * p.ldv + h * p.vdim + j, v);
+    }
+    return;
+  }
+  const bool is_q = uu < p.q_heads;
+  const int h = is_q ? uu : uu - p.q_heads;
+  const int col = (is_q ? p.q_off : p.k_off) + h * p.dim;
+  const int64_t orow = is_q ? n : (p.slot_mapping ? p.slot_mapping[n] : n);
+  if (orow < 0) return;
+  float ss = 0.f;
+  for (int j = lane; j < p.dim; j += 32) {
+    const float v = in[col + j] + (p.bias ? __ldg(p.bias + col + j) : 0.f);
+    x[j] = v;
+    ss += v * v;
+  }
+  const float* nw = is_q ? p.q_norm : p.k_norm;
+  float r = 1.f;
+  if (nw) {
+    ss = warp_sum(ss);
+    r = 1.0f / sqrtf(ss / (float)p.dim + p.eps);
+  }
+  __syncwarp();
+  const int half = p.rot_dims >> 1;
+  const float2* tab = reinterpret_cast<const float2*>(p.rot_table) + (int64_t)(p.rot_dims ? p.positions[n] : 0) * half;
+  const float post = is_q ? 1.f : p.k_scale;
+  for (int j = lane; j < p.dim; j += 32) {
+    float y = x[j] * r * (nw ? __ldg(nw + j) : 1.f);
+    if (j < p.rot_dims) {
+      int i, partner;
+      float sign;
+      if (p.rot_half) { i = j < half ? j : j - half; partner = j < half ? j + half : j - half; sign = j < half ? -1.f : 1.f; }
+      else { i = j >> 1; partner = j ^ 1; sign = (j & 1) ? 1.f : -1.f; }
+      const float2 cs = __ldg(tab + i);
+      const float z = x[partner] * r * (nw ? __ldg(nw + partner) : 1.f);
+      y = y * cs.x + sign * z * cs.y;
+    }
+    y *= post;
+    if (is_q) st_f(reinterpret_cast<TQ*>(p.q_out) + orow * p.ldq + h * p.dim + j, y);
+    else st_f(reinterpret_cast<TKV*>(p.k_out) + orow * p.ldk + h * p.dim + j, y);
+  }
+}
+
+template <typename TQ, typename TKV>
+int launch_prep(nvc_ctx* ctx, const nvc_qkv_prep* p, int N, void* stream) {
+  PrepArgs a{*p, N};
+  const int64_t units = (int64_t)N * (p->q_heads + 2 * p->kv_heads);
+  const int wmax = p->dim > p->vdim ? p->dim : p->vdim;
+  NVC_CUDA_CHECK(ctx, nvc_launch(ctx, qkv_prep_kernel<TQ, TKV>, dim3((unsigned)((units + 3) / 4)), dim3(128), (size_t)4 * wmax * sizeof(float),
+                                 nvc_stream(stream), a));
+  ctx->launches++;
+  return NVC_OK;
+}
+
+}  // namespace
+
+extern "C" int nvc_qkv_prep_run(nvc_ctx* ctx, const nvc_qkv_prep* p, int N, void* stream) {
+  NVC_REQUIRE(ctx, ctx && p && p->in && p->q_out && p->k_out && p->v_out, NVC_EINVAL, "null pointer");
+  NVC_REQUIRE(ctx, N >= 0 && p->q_heads > 0 && p->kv_heads > 0 && p->dim > 0 && p->vdim > 0 && p->dim <= 2048 && p->vdim <= 2048,
+              NVC_EINVAL, "bad sizes");
+  NVC_REQUIRE(ctx, p->rot_dims >= 0 && p->rot_dims % 2 == 0 && p->rot_dims <= p->dim && (p->rot_dims == 0 || (p->rot_table && p->positions)),
+              NVC_EINVAL, "bad rotary arguments");
+  NVC_REQUIRE(ctx, (p->q_norm == nullptr) == (p->k_norm == nullptr), NVC_EINVAL, "q and k norms come together");
+  NVC_REQUIRE(ctx, p->blend == NVC_BLEND_NONE || (p->v_first && p->ldvf >= p->kv_heads * p->vdim && (p->blend != NVC_BLEND_MIX || p->lambda)),
+              NVC_EINVAL, "value blending needs its buffer and weight");
+  NVC_REQUIRE(ctx, p->ldq >= p->q_heads * p->dim && p->ldk >= p->kv_heads * p->dim && p->ldv >= p->kv_heads * p->vdim, NVC_EINVAL,
+              "bad strides");
+  if (N == 0) return NVC_OK;
+  if (p->q_dtype == NVC_DT_F32 && p->kv_dtype == NVC_DT_F32) return launch_prep<float, float>(ctx, p, N, stream);
+  if (p->q_dtype == NVC_DT_BF16 && p->kv_dtype == NVC_DT_BF16) return launch_prep<__nv_bfloat16, __nv_bfloat16>(ctx, p, N, stream);
+  if (p->q_dtype == NVC_DT_BF16 && p->kv_dtype == NVC_DT_F32) return launch_prep<__nv_bfloat16, float>(ctx, p, N, stream);
+  return launch_prep<float, __nv_bfloat16>(ctx, p, N, stream);
+}
+
+// (cos, sin) of position * base^(-2 i / dims) for every position below max_pos and i < dims / 2, angles in double precision.
+// Synchronous (called once, when a model is built).
+extern "C" int nvc_rotary_table_init_sync(nvc_ctx* ctx, float base, int dims, int max_pos, float* out) {
+  NVC_REQUIRE(ctx, ctx && out && dims > 0 && dims % 2 == 0 && max_pos > 0 && base > 0.f, NVC_EINVAL, "bad arguments");
+  const int half = dims / 2;
+  std::string buf((size_t)max_pos * half * 2 * sizeof(float), '\0');
+  float* h = reinterpret_cast<float*>(&buf[0]);
+  for (int i = 0; i < half; ++i) {
+    const double f = pow((double)base, -2.0 * (double)i / (double)dims);
+    for (int p = 0; p < max_pos; ++p) {
+      const double ang = (double)p * f;
+      h[((size_t)p * half + i) * 2] = (float)cos(ang);
+      h[((size_t)p * half + i) * 2 + 1] = (float)sin(ang);
+    }
+  }
+  NVC_CUDA_CHECK(ctx, cudaMemcpy(out, h, buf.size(), cudaMemcpyHostToDevice));
+  return NVC_OK;
+}

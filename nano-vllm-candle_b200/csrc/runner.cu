@@ -255,6 +255,23 @@ int stage_sampling(nvc_runner* r, int B) {
   return NVC_OK;
 }
 
+// Bodies with recurrent state: the step's sequences must have been given their state slots (one step only).  Copies them to
+// dst (pinned staging) and disarms; NVC_OK with *used = false when the body has no state.
+int take_state_slots(nvc_runner* r, int B, int32_t* dst, bool* used) {
+  const int slots = r->body ? r->body->num_state_slots() : 0;
+  const int armed = r->state_slots_armed;
+  r->state_slots_armed = 0;
+  *used = slots > 0;
+  if (slots == 0) return NVC_OK;
+  NVC_REQUIRE(r->ctx, armed == B, NVC_ESTATE, "this model keeps recurrent state: nvc_runner_set_state_slots must name the slot of every sequence of the step");
+  for (int b = 0; b < B; ++b) {
+    NVC_REQUIRE(r->ctx, r->armed_state_slots[b] >= 0 && r->armed_state_slots[b] < slots, NVC_EINVAL, "state slot out of range");
+    for (int c = 0; c < b; ++c) NVC_REQUIRE(r->ctx, r->armed_state_slots[c] != r->armed_state_slots[b], NVC_EINVAL, "two sequences share a state slot");
+    dst[b] = r->armed_state_slots[b];
+  }
+  return NVC_OK;
+}
+
 // step inputs, their pinned staging and the sampling state: what every model family needs
 int alloc_step_buffers(nvc_runner* r) {
   const nvc_runner_options* opt = &r->opt;
@@ -265,11 +282,12 @@ int alloc_step_buffers(nvc_runner* r) {
   {
     r->in_pitch = (std::max(T, Bm) + 3) / 4 * 4;
     int32_t* blk = nullptr;
-    if ((rc = dev_alloc(r, &blk, 4 * r->in_pitch))) return rc;
+    if ((rc = dev_alloc(r, &blk, 5 * r->in_pitch))) return rc;
     r->d_ids = blk;
     r->d_pos = blk + r->in_pitch;
     r->d_slots = blk + 2 * r->in_pitch;
     r->d_ctx = blk + 3 * r->in_pitch;
+    r->d_state_slots = blk + 4 * r->in_pitch;
   }
   if ((rc = dev_alloc(r, &r->d_cu, Bm + 1))) return rc;
   if ((rc = dev_alloc(r, &r->d_cu2, Bm + 1))) return rc;
@@ -282,7 +300,7 @@ int alloc_step_buffers(nvc_runner* r) {
   if ((rc = dev_alloc(r, &r->d_streams, Bm))) return rc;
   R_CUDA(cudaMallocHost(&r->h_temps, Bm * sizeof(float)));
   R_CUDA(cudaMallocHost(&r->h_streams, Bm * sizeof(uint64_t)));
-  r->h_stage_ints = 3 * T + 2 * (Bm + 1) + Bm * r->max_blocks_cap + 2 * Bm + (size_t)r->max_logit_rows;
+  r->h_stage_ints = 3 * T + 2 * (Bm + 1) + Bm * r->max_blocks_cap + 3 * Bm + (size_t)r->max_logit_rows;
   R_CUDA(cudaMallocHost(&r->h_stage, r->h_stage_ints * sizeof(int32_t)));
   r->bt_mirror.assign(Bm * r->max_blocks_cap, -1);
   R_CUDA(cudaMallocHost(&r->h_pairs, Bm * tp * sizeof(ArgPair)));
@@ -604,6 +622,13 @@ int prefill_impl(nvc_runner* r, const int32_t* ids, const int32_t* positions, co
   int32_t* armed = h + r->h_stage_ints - r->max_logit_rows;   // the tail of the staging block
   if (use_armed) memcpy(armed, r->armed_rows.data(), (size_t)rows * 4);
   cudaStream_t st = r->stream;
+  {
+    int32_t* hss = armed - B;      // in front of the armed rows
+    bool has_state = false;
+    int rcs = take_state_slots(r, B, hss, &has_state);
+    if (rcs) return rcs;
+    if (has_state) R_CUDA(cudaMemcpyAsync(r->d_state_slots, hss, (size_t)B * 4, cudaMemcpyHostToDevice, st));
+  }
   R_CUDA(cudaMemcpyAsync(r->d_ids, h, N * 4, cudaMemcpyHostToDevice, st));
   R_CUDA(cudaMemcpyAsync(r->d_pos, h + N, N * 4, cudaMemcpyHostToDevice, st));
   R_CUDA(cudaMemcpyAsync(r->d_slots, h + 2 * N, N * 4, cudaMemcpyHostToDevice, st));
@@ -722,10 +747,16 @@ extern "C" int nvc_runner_decode(nvc_runner* r, const int32_t* ids, const int32_
   memcpy(h + B, positions, B * 4);
   memcpy(h + 2 * B, slot_mapping, B * 4);
   memcpy(h + 3 * B, context_lens, B * 4);
+  bool has_state = false;
+  {
+    int rcs = take_state_slots(r, B, h + 4 * B, &has_state);
+    if (rcs) return rcs;
+  }
+  const int in_rows = has_state ? 5 : 4;
   cudaStream_t st = r->stream;
   // block table: the device copy is kept between decode steps; a row changes only when a sequence crosses a block
   // boundary or the batch changes, so most steps upload (and validate) nothing but the 4 x B scalars above
-  int32_t* hbt = h + 4 * B;
+  int32_t* hbt = h + 5 * B;
   const int cap = r->max_blocks_cap;
   bool bt_changed = r->bt_mirror_B != B;
   for (int b = 0; b < B; ++b) {
@@ -734,7 +765,7 @@ extern "C" int nvc_runner_decode(nvc_runner* r, const int32_t* ids, const int32_
     for (int j = max_blocks; j < cap; ++j) row[j] = -1;
     bt_changed = bt_changed || memcmp(row, r->bt_mirror.data() + (size_t)b * cap, (size_t)cap * 4) != 0;
   }
-  r->last_h2d_bytes = (int64_t)B * 16;
+  r->last_h2d_bytes = (int64_t)B * 4 * in_rows;
   if (bt_changed) {
     for (int b = 0; b < B; ++b)
       for (int j = 0; j < max_blocks; ++j) {
@@ -753,7 +784,7 @@ extern "C" int nvc_runner_decode(nvc_runner* r, const int32_t* ids, const int32_
   // the whole step - one strided H2D of the four input rows, the sampling parameters, the kernels, the D2H of the
   // tokens - is ONE graph launch: the host touches pinned memory, launches, and waits
   auto whole_step = [&]() -> int {
-    cudaError_t ce = cudaMemcpy2DAsync(r->d_ids, r->in_pitch * 4, h, (size_t)B * 4, (size_t)B * 4, 4, cudaMemcpyHostToDevice, st);
+    cudaError_t ce = cudaMemcpy2DAsync(r->d_ids, r->in_pitch * 4, h, (size_t)B * 4, (size_t)B * 4, in_rows, cudaMemcpyHostToDevice, st);
     if (ce != cudaSuccess) return NVC_CUDA_ERROR_BASE + (int)ce;
     int rc2 = stage_sampling(r, B);
     if (rc2) return rc2;
@@ -984,6 +1015,7 @@ extern "C" int nvc_runner_time_op(nvc_runner* r, int op, int iters, float* ms_pe
 // registry models
 // ------------------------------------------------------------------------------------------
 nvc_model_body* nvc_make_karuzen_body(nvc_runner* r, const nvc_karuzen_config& cfg, int* status);   // model_karuzen.cu
+nvc_model_body* nvc_make_ranilix_body(nvc_runner* r, const nvc_ranilix_config& cfg, int* status);   // model_ranilix.cu
 
 extern "C" int nvc_runner_create_from_config(nvc_ctx* ctx, const nvc_model_config* mc, const nvc_runner_options* opt,
                                              nvc_runner** out) {
@@ -993,8 +1025,9 @@ extern "C" int nvc_runner_create_from_config(nvc_ctx* ctx, const nvc_model_confi
     NVC_REQUIRE(ctx, opt->dtype == NVC_DT_BF16, NVC_ENOTIMPL, "the Qwen3 body runs in bf16 only");
     return nvc_runner_create(ctx, &mc->qwen3, opt, out);
   }
-  NVC_REQUIRE(ctx, mc->architecture == "Karuzen", NVC_ENOTIMPL, "architecture " + mc->architecture + " has no model body");
-  NVC_REQUIRE(ctx, ctx->tp_size == 1, NVC_ENOTIMPL, "Karuzen runs on one GPU");
+  NVC_REQUIRE(ctx, mc->architecture == "Karuzen" || mc->architecture == "Ranilix", NVC_ENOTIMPL,
+              "architecture " + mc->architecture + " has no model body");
+  NVC_REQUIRE(ctx, ctx->tp_size == 1, NVC_ENOTIMPL, mc->architecture + " runs on one GPU");
   NVC_REQUIRE(ctx, opt->dtype == NVC_DT_BF16 || opt->dtype == NVC_DT_F32, NVC_EINVAL, "dtype must be NVC_DT_BF16 or NVC_DT_F32");
   NVC_REQUIRE(ctx, opt->num_kvcache_blocks > 0 && opt->kvcache_block_size > 0 && opt->max_num_seqs > 0 &&
                        opt->max_num_batched_tokens > 0 && opt->max_model_len > 0, NVC_EINVAL, "bad runner options");
@@ -1010,7 +1043,7 @@ extern "C" int nvc_runner_create_from_config(nvc_ctx* ctx, const nvc_model_confi
   *out = r;
   R_CUDA(cudaStreamCreateWithFlags(&r->stream, cudaStreamNonBlocking));
   int rc = NVC_OK;
-  r->body = nvc_make_karuzen_body(r, mc->karuzen, &rc);
+  r->body = mc->architecture == "Ranilix" ? nvc_make_ranilix_body(r, mc->ranilix, &rc) : nvc_make_karuzen_body(r, mc->karuzen, &rc);
   if (rc) return rc;
   r->V_l = r->body->vocab();
   if ((rc = dev_alloc(r, &r->logits, (size_t)r->max_logit_rows * r->body->logits_ld()))) return rc;
@@ -1049,6 +1082,15 @@ extern "C" int nvc_runner_set_residual_tap(nvc_runner* r, float* host, int64_t c
   if (!r) return NVC_EINVAL;
   NVC_REQUIRE(r->ctx, r->body, NVC_ENOTIMPL, "the residual tap needs a registry model");
   return r->body->set_residual_tap(host, (size_t)std::max<int64_t>(capacity_floats, 0));
+}
+extern "C" int nvc_runner_num_state_slots(const nvc_runner* r) { return r && r->body ? r->body->num_state_slots() : 0; }
+extern "C" int nvc_runner_set_state_slots(nvc_runner* r, const int32_t* slots, int B) {
+  if (!r) return NVC_EINVAL;
+  if (!slots) { r->state_slots_armed = 0; return NVC_OK; }
+  NVC_REQUIRE(r->ctx, B > 0 && B <= r->opt.max_num_seqs, NVC_EINVAL, "bad batch size");
+  r->armed_state_slots.assign(slots, slots + B);
+  r->state_slots_armed = B;
+  return NVC_OK;
 }
 extern "C" int nvc_runner_layer_runs(const nvc_runner* r) { return r && r->body ? r->body->layer_runs() : 0; }
 extern "C" int nvc_runner_width(const nvc_runner* r) { return !r ? 0 : (r->body ? r->body->width() : r->cfg.hidden_size); }

@@ -28,7 +28,7 @@ struct nvc_step_shape {
   int max_chunk = 1;
 };
 
-// A model family behind the runner.  Implementations: model_karuzen.cu.
+// A model family behind the runner.  Implementations: model_karuzen.cu, model_ranilix.cu.
 struct nvc_model_body {
   virtual ~nvc_model_body() {}
   // one tensor of the checkpoint, in its own dtype (NVC_ST_*), host memory; shape has ndim entries
@@ -48,6 +48,10 @@ struct nvc_model_body {
   virtual const char* profile_json() const { return "{}"; }
   virtual int layer_runs() const { return 0; }
   virtual int width() const { return 0; }
+  // > 0: the body keeps per-sequence recurrent state in that many slots; every step then names the slot of each of its
+  // sequences (r->d_state_slots [B], armed with nvc_runner_set_state_slots), and a sequence whose first token of a step sits
+  // at position 0 starts from an empty state
+  virtual int num_state_slots() const { return 0; }
 };
 
 struct nvc_qwen3_layer {
@@ -85,6 +89,9 @@ struct nvc_runner {
   void* decode_ws = nullptr;
   size_t decode_ws_bytes = 0;
   // step inputs on device + pinned staging
+  int32_t* d_state_slots = nullptr;   // state slot of every sequence of the step (bodies with recurrent state)
+  std::vector<int32_t> armed_state_slots;
+  int state_slots_armed = 0;          // > 0: nvc_runner_set_state_slots named the slots of the next step's sequences
   int32_t* d_cu2 = nullptr;     // mixed step: cu_seqlens of the prompt chunks, relative to their first token
   int32_t *d_ids = nullptr, *d_pos = nullptr, *d_cu = nullptr, *d_slots = nullptr, *d_bt = nullptr, *d_ctx = nullptr,
           *d_last_rows = nullptr, *d_tok = nullptr;
@@ -92,7 +99,7 @@ struct nvc_runner {
   nvc_arg_pair* d_pairs = nullptr;
   int32_t* h_stage = nullptr;   // pinned
   size_t h_stage_ints = 0;
-  size_t in_pitch = 0;             // ints between d_ids / d_pos / d_slots / d_ctx (one block: a decode step uploads all four in ONE 2-D copy)
+  size_t in_pitch = 0;             // ints between d_ids / d_pos / d_slots / d_ctx (one block, d_state_slots behind them: a decode step uploads them in ONE 2-D copy)
   std::vector<int32_t> bt_mirror;  // the padded block table the device holds (decode steps re-upload it only when it changed)
   int bt_mirror_B = -1;            // rows of bt_mirror that are valid; -1: unknown (a prefill / mixed step wrote d_bt)
   nvc_arg_pair* h_pairs = nullptr;   // pinned

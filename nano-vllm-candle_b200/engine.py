@@ -337,7 +337,7 @@ class Qwen3ModelRunner:
 
 class ModelRunner(Qwen3ModelRunner):
     """A runner for any registered architecture, chosen by config.json (the model registry lives in the library:
-    "Qwen3ForCausalLM" -> the Qwen3 body, "Karuzen" -> the Karuzen body).  Same step methods as
+    "Qwen3ForCausalLM" -> the Qwen3 body, "Karuzen" and "Ranilix" -> their bodies).  Same step methods as
     Qwen3ModelRunner; registry models attend through the paged cache, so their steps are `decode`
     and `step_mixed` (the engine drives them the same way).
 
@@ -439,6 +439,16 @@ class ModelRunner(Qwen3ModelRunner):
             return
         a = _i32(rows)
         check(self.l.nvc_runner_set_logit_rows(self.handle, _p(a), len(a)), "nvc_runner_set_logit_rows", self.ctx.h)
+
+    def num_state_slots(self) -> int:
+        """> 0: the model keeps per-sequence recurrent state in that many slots (see set_state_slots)."""
+        return self.l.nvc_runner_num_state_slots(self.handle)
+
+    def set_state_slots(self, slots) -> None:
+        """Names the state slot of every sequence of the NEXT step, in batch order (models with recurrent state; the
+        engine does this by itself)."""
+        a = _i32(slots)
+        check(self.l.nvc_runner_set_state_slots(self.handle, _p(a), len(a)), "nvc_runner_set_state_slots", self.ctx.h)
 
     def last_logits(self, B: int) -> np.ndarray:
         out = np.empty((B, self.vocab_size // self.ctx.tp_size), dtype=np.float32)
