@@ -107,6 +107,13 @@ def _declare(l: C.CDLL) -> None:
         "nvc_gemm_bf16_grouped": [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _i, _vp],
         "nvc_moe_combine": [_vp, _vp, _i, _i, _vp, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _vp],
         "nvc_latent_attn_paged": [_vp, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _i, _i, _vp, _sz, _vp],
+        "nvc_embed_gather_scaled_f32": [_vp, _vp, _vp, _i, _i, _f, _vp, _i, _i, _i, _vp],
+        "nvc_rms_norm_pair": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _f, _vp, _i, _i, _vp],
+        "nvc_head_gate": [_vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _f, _i, _f, _i, _vp],
+        "nvc_rotary_table_init_sync": [_vp, _f, _i, _i, _vp],
+        "nvc_qkv_prep_run": [_vp, _vp, _i, _vp],
+        "nvc_attn_paged_wide": [_vp, _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _i, _i, _vp],
+        "nvc_retention_scan": [_vp, _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
         "nvc_debug_set": [_i, _i],
     }
     for name, args in sigs.items():

@@ -476,3 +476,92 @@ def latent_attn_paged(ctx, q, cache, block_tables, context_lens, cu_seqlens, max
                                       workspace.numel() * workspace.element_size() if workspace is not None else 0, _stream()),
           "nvc_latent_attn_paged", ctx.h)
     return out
+
+
+# ---------------------------------------------------------------- RMS-norm pair, q / k / v preparation, wide attention, retention
+class QkvPrepC(C.Structure):
+    """nvc_qkv_prep of include/nvc_b200.h."""
+    _fields_ = [("in_", C.c_void_p), ("ldi", C.c_int), ("bias", C.c_void_p), ("q_off", C.c_int), ("k_off", C.c_int), ("v_off", C.c_int),
+                ("q_heads", C.c_int), ("kv_heads", C.c_int), ("dim", C.c_int), ("vdim", C.c_int), ("q_norm", C.c_void_p),
+                ("k_norm", C.c_void_p), ("eps", C.c_float), ("rot_dims", C.c_int), ("rot_half", C.c_int), ("rot_table", C.c_void_p),
+                ("positions", C.c_void_p), ("k_scale", C.c_float), ("blend", C.c_int), ("lambda_", C.c_void_p), ("v_first", C.c_void_p),
+                ("ldvf", C.c_int), ("q_out", C.c_void_p), ("ldq", C.c_int), ("k_out", C.c_void_p), ("v_out", C.c_void_p), ("ldk", C.c_int),
+                ("ldv", C.c_int), ("slot_mapping", C.c_void_p), ("q_dtype", C.c_int), ("kv_dtype", C.c_int)]
+
+
+class AttnSpecC(C.Structure):
+    """nvc_attn_spec of include/nvc_b200.h."""
+    _fields_ = [("heads", C.c_int), ("kv_heads", C.c_int), ("dim", C.c_int), ("vdim", C.c_int), ("scale", C.c_float), ("window", C.c_int),
+                ("sink", C.c_void_p), ("gate", C.c_void_p), ("ldg", C.c_int), ("out_scale", C.c_float)]
+
+
+def _a(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def embed_gather_scaled_f32(ctx, ids, table, scale: float):
+    out = torch.empty(ids.numel(), table.shape[1], dtype=torch.float32, device=table.device)
+    check(ctx.l.nvc_embed_gather_scaled_f32(ctx.h, _ptr(ids), _ptr(table), _dt(table), table.stride(0), scale, _ptr(out), out.stride(0),
+                                            ids.numel(), table.shape[1], _stream()), "nvc_embed_gather_scaled_f32", ctx.h)
+    return out
+
+
+def rms_norm_pair(ctx, res, addends, w0, w1=None, eps: float = 1e-5, out_dtype=torch.float32, rows=None, write_back: bool = True):
+    """(residual after the sums - a new tensor, or None when rows gather or write_back is False; out0; out1)."""
+    a0, a1 = (list(addends) + [None, None])[:2]
+    N = res.shape[0] if rows is None else rows.numel()
+    H = res.shape[1]
+    res_out = torch.empty_like(res) if (rows is None and write_back) else None
+    out0 = torch.empty(N, H, dtype=out_dtype, device=res.device) if w0 is not None else None
+    out1 = torch.empty(N, H, dtype=out_dtype, device=res.device) if w1 is not None else None
+    check(ctx.l.nvc_rms_norm_pair(ctx.h, _ptr(res), _ptr(a0), _ptr(a1), _ptr(res_out), res.stride(0), _ptr(w0), _ptr(out0), _ptr(w1),
+                                  _ptr(out1), 0 if out_dtype == torch.bfloat16 else 1, H, eps, _ptr(rows), N, H, _stream()),
+          "nvc_rms_norm_pair", ctx.h)
+    return res_out, out0, out1
+
+
+def head_gate(ctx, o, gate, heads: int, vdim: int, norm: bool, eps: float, act: str, out_scale: float, out_dtype=torch.float32):
+    out = torch.empty(o.shape[0], heads * vdim, dtype=out_dtype, device=o.device)
+    check(ctx.l.nvc_head_gate(ctx.h, _ptr(o), o.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(out), out.stride(0),
+                              0 if out_dtype == torch.bfloat16 else 1, heads, vdim, 1 if norm else 0, eps, {"sigmoid": 0, "silu": 1}[act],
+                              out_scale, o.shape[0], _stream()), "nvc_head_gate", ctx.h)
+    return out
+
+
+def rotary_table(ctx, base: float, dims: int, max_pos: int, device="cuda:0"):
+    out = torch.empty(max_pos, dims // 2, 2, dtype=torch.float32, device=device)
+    check(ctx.l.nvc_rotary_table_init_sync(ctx.h, base, dims, max_pos, _ptr(out)), "nvc_rotary_table_init_sync", ctx.h)
+    return out
+
+
+def qkv_prep(ctx, x, q_off, k_off, v_off, q_heads, kv_heads, dim, vdim, q_out, k_out, v_out, *, bias=None, q_norm=None, k_norm=None,
+             eps=1e-5, rot_dims=0, rot_half=False, rot_table=None, positions=None, k_scale=1.0, blend=0, lam=None, v_first=None,
+             slot_mapping=None):
+    """x: fp32 [N, ld] rows of a fused projection; q_out [N, q_heads * dim]; k_out / v_out: cache rows (slot_mapping) or [N, ...]."""
+    p = QkvPrepC(_a(x), x.stride(0), _a(bias), q_off, k_off, v_off, q_heads, kv_heads, dim, vdim, _a(q_norm), _a(k_norm), eps, rot_dims,
+                 1 if rot_half else 0, _a(rot_table), _a(positions), k_scale, blend, _a(lam), _a(v_first),
+                 v_first.stride(0) if v_first is not None else 0, _a(q_out), q_out.stride(0), _a(k_out), _a(v_out), k_out.stride(0),
+                 v_out.stride(0), _a(slot_mapping), _dt(q_out), _dt(k_out))
+    check(ctx.l.nvc_qkv_prep_run(ctx.h, C.byref(p), x.shape[0], _stream()), "nvc_qkv_prep_run", ctx.h)
+
+
+def attn_paged_wide(ctx, q, k_cache, v_cache, block_tables, context_lens, cu_seqlens, max_qlen: int, block_size: int, heads: int,
+                    kv_heads: int, dim: int, vdim: int, scale: float, window: int = 0, sink=None, gate=None, out_scale: float = 1.0):
+    """q: [rows, heads * dim]; k_cache [slots, kv_heads * dim], v_cache [slots, kv_heads * vdim]; returns [rows, heads * vdim]."""
+    rows = q.shape[0]
+    out = torch.empty(rows, heads * vdim, dtype=q.dtype, device=q.device)
+    sp = AttnSpecC(heads, kv_heads, dim, vdim, scale, window, _a(sink), _a(gate), gate.stride(0) if gate is not None else 0, out_scale)
+    check(ctx.l.nvc_attn_paged_wide(ctx.h, _ptr(q), q.stride(0), _ptr(k_cache), k_cache.stride(0), _ptr(v_cache), v_cache.stride(0),
+                                    _ptr(block_tables), block_tables.stride(0), _ptr(context_lens), _ptr(cu_seqlens), context_lens.numel(),
+                                    rows, max_qlen, block_size, C.byref(sp), _ptr(out), out.stride(0), _dt(q), _stream()),
+          "nvc_attn_paged_wide", ctx.h)
+    return out
+
+
+def retention_scan(ctx, q, k, v, state, state_slots, cu_seqlens, positions, decay, heads: int, dim: int, vdim: int):
+    """q, k: fp32 [N, heads * dim]; v: fp32 [N, heads * vdim]; state: fp32 [slots, heads, dim, vdim], updated in place."""
+    o = torch.empty(q.shape[0], heads * vdim, dtype=torch.float32, device=q.device)
+    check(ctx.l.nvc_retention_scan(ctx.h, _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(o), o.stride(0), _ptr(state),
+                                   _ptr(state_slots), _ptr(cu_seqlens), _ptr(positions), _ptr(decay), state_slots.numel(), heads, dim, vdim,
+                                   _stream()), "nvc_retention_scan", ctx.h)
+    return o

@@ -110,7 +110,7 @@ def windowed_attention(h, p: Dict[str, torch.Tensor], m: dict, eps: float, pos0:
     v_own = v
     if v_first is not None:
         lam = p["vmix"]
-        v = (1.0 - lam) * v + lam * v_first
+        v = (1.0 - lam) * v + lam * v_first.reshape(T, G, vd)      # head by head when the shapes agree, else as one flat row
     if kv_prefix is not None:
         k = torch.cat([kv_prefix[0], k], 0)
         v = torch.cat([kv_prefix[1], v], 0)
