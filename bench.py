@@ -523,15 +523,15 @@ _OUT = None
 
 
 def run_compare_families(args):
-    """Karuzen beside the closest existing family at equal layer sizes (nano-vllm-candle_b200/family_bench.py)."""
+    """A registry family beside the closest existing family at equal layer sizes (nano-vllm-candle_b200/family_bench.py)."""
     import torch
     ops = importlib.import_module("nano-vllm-candle_b200.ops")
     fb = importlib.import_module("nano-vllm-candle_b200.family_bench")
     pk = _peaks()
     ctx = ops.Context(0)
     sizes = [s for s in fb.SIZES if not args.compare_sizes or s["name"] in args.compare_sizes.split(",")]
-    line = fb.compare(ctx, sizes=sizes, K=min(args.steps, 64), W=max(args.warmup, 3),
-                      peaks={"bf16": pk["bf16_burst"], "hbm": pk["hbm_gbs"], "source": pk["source"]})
+    line = fb.compare(ctx, sizes=sizes, K=min(args.steps, 64), W=max(args.warmup, 3), family=args.compare_family,
+                      peaks={"bf16": pk["bf16_burst"], "hbm": pk["hbm_gbs"], "source": pk["source"], "fp32": 72.7})
     ctx.close()
     _emit(line)
 
@@ -558,8 +558,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-north-star", action="store_true", help="skip the Qwen3-8B batch-256 sub-record")
     ap.add_argument("--compare-families", action="store_true",
-                    help="instead of the headline workload: Karuzen beside Qwen3 at equal layer sizes (prefill / decode throughput, "
+                    help="instead of the headline workload: a registry family (--compare-family) beside Qwen3 at equal layer sizes (prefill / decode throughput, "
                          "per-op rooflines), one JSON line; 1 GPU")
+    ap.add_argument("--compare-family", default="karuzen", choices=["karuzen", "ranilix"],
+                    help="with --compare-families: which registry family stands beside Qwen3")
     ap.add_argument("--compare-sizes", default="", help="with --compare-families: comma-separated size names (default: all)")
     args = ap.parse_args()
     if args.compare_families:

@@ -435,10 +435,11 @@ int nvc_attn_paged_wide(nvc_ctx* ctx, const void* q, int ldq, const void* k_cach
 /* Retention: S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t per head over the new tokens of every sequence (rows
  * cu_seqlens[b] .. cu_seqlens[b + 1], or row b when cu_seqlens == NULL).  state: fp32 [slots, heads, dim, vdim]; sequence b
  * uses slot state_slots[b], starts from zeros when positions[first row] == 0 and leaves its last state in the slot.
- * q, k, v, o: fp32 rows. */
+ * q, k, v, o: fp32 rows.  max_qlen: the longest portion; above 4 tokens the recurrence runs 32 tokens at a time (the same
+ * sums regrouped, fp32 FMA), else token by token. */
 int nvc_retention_scan(nvc_ctx* ctx, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, float* o, int ldo,
                        float* state, const int32_t* state_slots, const int32_t* cu_seqlens, const int32_t* positions,
-                       const float* decay, int B, int heads, int dim, int vdim, void* stream);
+                       const float* decay, int B, int max_qlen, int heads, int dim, int vdim, void* stream);
 
 /* K8. Replaces Qwen3ModelRunner::argmax (src/engine/llm_engine.rs:135-142) on device:
  * idx[b] = LAST index of the maximum of logits[b, :] (Iterator::max_by tie rule);

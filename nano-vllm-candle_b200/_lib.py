@@ -113,7 +113,7 @@ def _declare(l: C.CDLL) -> None:
         "nvc_rotary_table_init_sync": [_vp, _f, _i, _i, _vp],
         "nvc_qkv_prep_run": [_vp, _vp, _i, _vp],
         "nvc_attn_paged_wide": [_vp, _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _i, _i, _vp],
-        "nvc_retention_scan": [_vp, _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+        "nvc_retention_scan": [_vp, _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
         "nvc_debug_set": [_i, _i],
     }
     for name, args in sigs.items():

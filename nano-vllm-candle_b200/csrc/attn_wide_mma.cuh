@@ -128,10 +128,12 @@ __device__ __forceinline__ void softmax_step(uint32_t stK, uint32_t stV, int tok
   }
   l0 = l0 * al0 + ps0;
   l1 = l1 * al1 + ps1;
+  if (__any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {      // a running maximum moved: rare after the first tiles
 #pragma unroll
-  for (int nt = 0; nt < NT; ++nt) {
-    o[nt][0] *= al0; o[nt][1] *= al0;
-    o[nt][2] *= al1; o[nt][3] *= al1;
+    for (int nt = 0; nt < NT; ++nt) {
+      o[nt][0] *= al0; o[nt][1] *= al0;
+      o[nt][2] *= al1; o[nt][3] *= al1;
+    }
   }
   {
     const int r = (lane & 7) + (((lane >> 3) & 1) << 3);
@@ -211,17 +213,43 @@ __global__ void __launch_bounds__(kWarps * 32) attn_wide_mma_kernel(const Args a
 #pragma unroll
   for (int i = 0; i < NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
-  // loads rows [tok0, tok0 + ntok) of K and V into a tile at `st` (K rows, then V rows at koff); rows past kmax are zero-filled
-  auto load_rows = [&](uint32_t st, uint32_t koff, int tok0, int ntok, int kmax, int tid, int nthreads) {
-    const int per_row = nck + ncv;
-    for (int idx = tid; idx < ntok * per_row; idx += nthreads) {
-      const int r = idx / per_row, c = idx - r * per_row;
-      const int tok = tok0 + r;
-      const uint32_t ok = tok <= kmax ? 16u : 0u;
-      const int tk = ok ? tok : tok0;
-      const int64_t slot = (int64_t)__ldg(bt + tk / a.block_size) * a.block_size + tk % a.block_size;
-      if (c < nck) cp_async16(st + r * RBK + ((c ^ (r & 7)) << 4), reinterpret_cast<const uint8_t*>(kc + slot * a.ldk) + c * 16, ok);
-      else cp_async16(st + koff + r * RBV + (((c - nck) ^ (r & 7)) << 4), reinterpret_cast<const uint8_t*>(vc + slot * a.ldv) + (c - nck) * 16, ok);
+  // One warp loads 16 consecutive tokens' K and V rows (tok0 a multiple of 16) into a tile at stK / stV.  Every lane owns one
+  // 16-byte chunk of a row - lanes [0, nck) a key chunk, lanes [nck, nck + ncv) a value chunk (nck + ncv <= 32) - so a row is one
+  // cp.async per lane.  With a block size that is a multiple of 16 the tile lies in one block: one table lookup per tile.
+  // Rows past kmax are zero-filled.
+  const bool lane_k = lane < nck, lane_on = lane < nck + ncv;
+  const int lc = lane_k ? lane : lane - nck;
+  const uint8_t* lane_src = lane_k ? reinterpret_cast<const uint8_t*>(kc) + lc * 16 : reinterpret_cast<const uint8_t*>(vc) + lc * 16;
+  const int64_t lane_pitch = lane_k ? (int64_t)a.ldk * 2 : (int64_t)a.ldv * 2;
+  const bool one_block = (a.block_size & 15) == 0;
+  auto load16 = [&](uint32_t stK, uint32_t stV, int tok0, int kmax) {
+    const uint32_t dst0 = lane_k ? stK : stV;
+    constexpr int RBmax = RBK > RBV ? RBK : RBV;
+    const uint32_t rb = lane_k ? RBK : RBV;
+    (void)RBmax;
+    if (one_block) {
+      const int tl = min(tok0, kmax);              // a tile wholly past kmax is zero-filled: look up a token that exists
+      const int64_t slot0 = (int64_t)__ldg(bt + tl / a.block_size) * a.block_size + tl % a.block_size;
+      const uint8_t* src = lane_src + slot0 * lane_pitch;
+      const int nvalid = kmax - tok0 + 1;          // rows of the tile that exist
+      if (lane_on) {
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+          const bool ok = r < nvalid;
+          cp_async16(dst0 + r * rb + ((lc ^ (r & 7)) << 4), ok ? src + r * lane_pitch : src, ok ? 16u : 0u);
+        }
+      }
+    } else {
+      int64_t my_slot = 0;
+      if (lane < 16) {
+        const int tk = min(tok0 + lane, kmax);
+        my_slot = (int64_t)__ldg(bt + tk / a.block_size) * a.block_size + tk % a.block_size;
+      }
+#pragma unroll 4
+      for (int r = 0; r < 16; ++r) {
+        const int64_t slot = __shfl_sync(0xffffffffu, my_slot, r);
+        if (lane_on) cp_async16(dst0 + r * rb + ((lc ^ (r & 7)) << 4), lane_src + slot * lane_pitch, tok0 + r <= kmax ? 16u : 0u);
+      }
     }
   };
   if (many) {
@@ -237,7 +265,10 @@ __global__ void __launch_bounds__(kWarps * 32) attn_wide_mma_kernel(const Args a
     const int n_tiles = kmax_cta / kCtaTok + 1 - tile0;
     const uint32_t ring = smem_u32(smem);
     auto issue = [&](int i) {
-      if (i < n_tiles) load_rows(ring + (i % kStages) * kTileBytes, kTileK, (tile0 + i) * kCtaTok, kCtaTok, kmax_cta, threadIdx.x, kWarps * 32);
+      if (i < n_tiles) {      // warp w brings rows 16 w .. 16 w + 15 of the 64-token tile
+        const uint32_t st = ring + (i % kStages) * kTileBytes;
+        load16(st + warp * 16 * RBK, st + kTileK + warp * 16 * RBV, (tile0 + i) * kCtaTok + warp * 16, kmax_cta);
+      }
       cp_async_commit();
     };
     issue(0);
@@ -250,7 +281,7 @@ __global__ void __launch_bounds__(kWarps * 32) attn_wide_mma_kernel(const Args a
       if (tok0 > kmax_w || tok0 + kCtaTok - 1 < kmin_w) continue;    // warp-uniform: nothing of this tile is visible to the warp
       const uint32_t st = ring + (i % kStages) * kTileBytes;
       const int nsub = min(kCtaTok / 16, (kmax_w - tok0) / 16 + 1);
-      const bool all_visible = tok0 >= lo_last && tok0 + kCtaTok - 1 <= first_w && r0 + 15 < total;
+      const bool all_visible = tok0 >= lo_last && tok0 + kCtaTok - 1 <= first_w;     // (rows past the end have q = 0: finite, never stored)
       softmax_step<DKM, DVM, kCtaTok / 16>(st, st + kTileK, tok0, nsub, ks_n, nt_n, qa, o, m0, m1, l0, l1, lo_a, hi_a, lo_b, hi_b, a.scale_log2e,
                                            all_visible, lane);
     }
@@ -261,11 +292,13 @@ __global__ void __launch_bounds__(kWarps * 32) attn_wide_mma_kernel(const Args a
     const int kmax = base + last_row / hg;
     const int kmin = a.window > 0 ? max(0, base + r0 / hg - a.window + 1) : 0;
     const int first = (kmin / kCtaTok) * kCtaTok + warp * 16;       // this warp's first 16-token tile
+    const int hi_first = base + r0 / hg;                            // the chunk's first row sees the least far ahead,
+    const int lo_last = a.window > 0 ? max(0, kmax - a.window + 1) : 0;   // its last row the least far back
     const int n_tiles = kmax >= first ? (kmax - first) / kCtaTok + 1 : 0;
     constexpr int kWarpStage = 16 * (RBK + RBV);
     const uint32_t ring = smem_u32(smem) + warp * (kStages * kWarpStage);
     auto issue = [&](int i) {
-      if (i < n_tiles) load_rows(ring + (i % kStages) * kWarpStage, 16 * RBK, first + i * kCtaTok, 16, kmax, lane, 32);
+      if (i < n_tiles) load16(ring + (i % kStages) * kWarpStage, ring + (i % kStages) * kWarpStage + 16 * RBK, first + i * kCtaTok, kmax);
       cp_async_commit();
     };
     issue(0);
@@ -275,8 +308,9 @@ __global__ void __launch_bounds__(kWarps * 32) attn_wide_mma_kernel(const Args a
       cp_async_wait<2>();
       __syncwarp();
       const uint32_t st = ring + (i % kStages) * kWarpStage;
-      softmax_step<DKM, DVM, 1>(st, st + 16 * RBK, first + i * kCtaTok, 1, ks_n, nt_n, qa, o, m0, m1, l0, l1, lo_a, hi_a, lo_b, hi_b,
-                                a.scale_log2e, false, lane);
+      const int tok0 = first + i * kCtaTok;
+      softmax_step<DKM, DVM, 1>(st, st + 16 * RBK, tok0, 1, ks_n, nt_n, qa, o, m0, m1, l0, l1, lo_a, hi_a, lo_b, hi_b, a.scale_log2e,
+                                tok0 >= lo_last && tok0 + 15 <= hi_first, lane);
       __syncwarp();
     }
     cp_async_wait<0>();

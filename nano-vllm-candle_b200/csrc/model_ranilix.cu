@@ -331,7 +331,7 @@ struct RanilixBody : nvc_body_base {
     if (rc) return rc;
     mark(r, "retention_prep");
     if ((rc = nvc_retention_scan(ctx, rq, qw, rk, qw, rv, vw, ro, vw, w.state, r->d_state_slots, s.decode ? nullptr : r->d_cu, r->d_pos, w.decay,
-                                 s.B, rt.heads, rt.dim, rt.vdim, r->stream)))
+                                 s.B, s.decode ? 1 : s.max_seqlen, rt.heads, rt.dim, rt.vdim, r->stream)))
       return rc;
     mark(r, "retention_scan");
     uint8_t* dst = reinterpret_cast<uint8_t*>(ao) + (size_t)w.lwp * esz;

@@ -5,9 +5,16 @@
 // its slot holds, and the slot is written back after the last token.  q, k, v, o are fp32 rows (the caller has already rotated q and
 // k and scaled k).
 //
-// One CTA per (sequence, head, slice of 32 value columns): thread (column v, row group r) keeps rows [r DPT, (r + 1) DPT) of column v
-// in registers; a token costs 2 DPT FMAs per thread and, when the rows are split, one shared-memory reduction.  The next token's q / k / v
-// are fetched while the current one is computed.
+// Two kernels, both with one CTA per (sequence, head, slice of 32 value columns) whose threads (column v, row group r) keep rows
+// [r DPT, (r + 1) DPT) of column v of the state in registers:
+//   retention_scan_kernel    token by token (decode steps and very short portions): 2 DPT FMAs per thread and token and, when the
+//                            rows are split, one shared-memory reduction; the next token's q / k / v are fetched meanwhile.
+//   retention_chunk_kernel   32 tokens at a time (prompt portions), the same recurrence regrouped:
+//                              A[t][j] = decay^(t - j) (q_t . k_j), j <= t            inside the chunk
+//                              o_t     = sum_j A[t][j] v_j + decay^(t + 1) S^T q_t     S: the state before the chunk
+//                              S      <- decay^n S + sum_j decay^(n - 1 - j) k_j v_j^T n: tokens of the chunk
+//                            Powers of the decay come from a table built by repeated multiplication (exact for 0 and 1).
+// Both are plain fp32 FMA code; they differ from one another by rounding only.
 #include "typed.cuh"
 
 namespace {
@@ -90,15 +97,141 @@ __global__ void retention_scan_kernel(const RetArgs a) {
       if (d0 + i < a.dim) sp[(int64_t)(d0 + i) * a.vdim + v] = S[i];
 }
 
+constexpr int kChunk = 32;          // tokens per chunk
+constexpr int kChunkWarps = 4;
+
+template <int DPT>
+__global__ void __launch_bounds__(kChunkWarps * 32) retention_chunk_kernel(const RetArgs a) {
+  extern __shared__ float sm[];
+  pdl_trigger();
+  const int b = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * 32;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int v = v0 + lane;
+  const bool vok = v < a.vdim;
+  const int dim = a.dim, qs = dim + 1;                 // row stride of the staged q (lane = token: conflict-free)
+  float* q_s = sm;                                     // [32][dim + 1]
+  float* k_s = q_s + kChunk * qs;                      // [32][dim]   (read as broadcasts)
+  float* v_s = k_s + kChunk * dim;                     // [32][32]
+  float* a_s = v_s + kChunk * 32;                      // [32][33]
+  float* part = a_s + kChunk * 33;                     // [warps][32][32]
+  float* gp = part + kChunkWarps * kChunk * 32;        // decay^0 .. decay^32
+  const float dec = __ldg(a.decay + h);
+  if (threadIdx.x == 0) {
+    float p = 1.f;
+    for (int i = 0; i <= kChunk; ++i) { gp[i] = p; p *= dec; }
+  }
+  pdl_wait();
+  const int r0 = a.cu_seqlens ? a.cu_seqlens[b] : b;
+  const int r1 = a.cu_seqlens ? a.cu_seqlens[b + 1] : b + 1;
+  const int d0 = w * DPT;
+  float S[DPT];
+  float* sp = a.state + (((int64_t)a.state_slots[b] * a.heads + h) * dim) * a.vdim;
+  const bool fresh = a.positions[r0] == 0;
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) S[i] = (!fresh && vok && d0 + i < dim) ? sp[(int64_t)(d0 + i) * a.vdim + v] : 0.f;
+  for (int c0 = r0; c0 < r1; c0 += kChunk) {
+    const int n = min(kChunk, r1 - c0);
+    __syncthreads();                                   // the previous chunk is done with the staged rows
+    for (int idx = threadIdx.x; idx < kChunk * dim; idx += blockDim.x) {
+      const int t = idx / dim, d = idx - t * dim;
+      const bool in = t < n;
+      q_s[t * qs + d] = in ? a.q[(int64_t)(c0 + t) * a.ldq + h * dim + d] : 0.f;
+      k_s[t * dim + d] = in ? a.k[(int64_t)(c0 + t) * a.ldk + h * dim + d] : 0.f;
+    }
+    for (int idx = threadIdx.x; idx < kChunk * 32; idx += blockDim.x) {
+      const int t = idx >> 5, c = idx & 31;
+      v_s[idx] = (t < n && v0 + c < a.vdim) ? a.v[(int64_t)(c0 + t) * a.ldv + h * a.vdim + v0 + c] : 0.f;
+    }
+    __syncthreads();
+    // ---- A[t][j]: lane = t, this warp's j = w, w + 4, ...
+    {
+      float acc[kChunk / kChunkWarps];
+#pragma unroll
+      for (int jj = 0; jj < kChunk / kChunkWarps; ++jj) acc[jj] = 0.f;
+      for (int d = 0; d < dim; ++d) {
+        const float qv = q_s[lane * qs + d];
+#pragma unroll
+        for (int jj = 0; jj < kChunk / kChunkWarps; ++jj) acc[jj] = fmaf(qv, k_s[(w + jj * kChunkWarps) * dim + d], acc[jj]);
+      }
+#pragma unroll
+      for (int jj = 0; jj < kChunk / kChunkWarps; ++jj) {
+        const int j = w + jj * kChunkWarps;
+        a_s[lane * 33 + j] = j <= lane ? acc[jj] * gp[lane - j] : 0.f;
+      }
+    }
+    // ---- the state's share of every output: this warp's rows of S against q_t, lane = value column
+    for (int t = 0; t < n; ++t) {
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < DPT; ++i)
+        if (d0 + i < dim) acc = fmaf(S[i], q_s[t * qs + d0 + i], acc);
+      part[(w * kChunk + t) * 32 + lane] = acc;
+    }
+    __syncthreads();
+    // ---- o_t for this warp's tokens t = w, w + 4, ...
+    for (int t = w; t < n; t += kChunkWarps) {
+      float acc = 0.f;
+      for (int j = 0; j <= t; ++j) acc = fmaf(a_s[t * 33 + j], v_s[j * 32 + lane], acc);
+      float cross = 0.f;
+#pragma unroll
+      for (int g = 0; g < kChunkWarps; ++g) cross += part[(g * kChunk + t) * 32 + lane];
+      if (vok) a.o[(int64_t)(c0 + t) * a.ldo + h * a.vdim + v] = fmaf(gp[t + 1], cross, acc);
+    }
+    // ---- the state after the chunk
+    {
+      const float gn = gp[n];
+#pragma unroll
+      for (int i = 0; i < DPT; ++i) S[i] *= gn;
+      for (int j = 0; j < n; ++j) {
+        const float vv = v_s[j * 32 + lane] * gp[n - 1 - j];
+#pragma unroll
+        for (int i = 0; i < DPT; ++i)
+          if (d0 + i < dim) S[i] = fmaf(k_s[j * dim + d0 + i], vv, S[i]);
+      }
+    }
+  }
+  if (vok)
+#pragma unroll
+    for (int i = 0; i < DPT; ++i)
+      if (d0 + i < dim) sp[(int64_t)(d0 + i) * a.vdim + v] = S[i];
+}
+
+template <int DPT>
+cudaError_t launch_chunk(nvc_ctx* ctx, const RetArgs& a, dim3 grid, size_t smem, cudaStream_t st) {
+  static bool attr_set = false;
+  if (!attr_set && smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(retention_chunk_kernel<DPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  return nvc_launch(ctx, retention_chunk_kernel<DPT>, grid, dim3(kChunkWarps * 32), smem, st, a);
+}
+
 }  // namespace
 
 extern "C" int nvc_retention_scan(nvc_ctx* ctx, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, float* o, int ldo,
                                   float* state, const int32_t* state_slots, const int32_t* cu_seqlens, const int32_t* positions,
-                                  const float* decay, int B, int heads, int dim, int vdim, void* stream) {
+                                  const float* decay, int B, int max_qlen, int heads, int dim, int vdim, void* stream) {
   NVC_REQUIRE(ctx, ctx && q && k && v && o && state && state_slots && positions && decay, NVC_EINVAL, "null pointer");
   NVC_REQUIRE(ctx, B > 0 && heads > 0 && dim > 0 && vdim > 0 && dim <= 1024 && heads <= 65535, NVC_EINVAL, "bad sizes");
   NVC_REQUIRE(ctx, ldq >= heads * dim && ldk >= heads * dim && ldv >= heads * vdim && ldo >= heads * vdim, NVC_EINVAL, "bad strides");
   RetArgs a{q, k, v, o, ldq, ldk, ldv, ldo, state, state_slots, cu_seqlens, positions, decay, heads, dim, vdim};
+  if (cu_seqlens && max_qlen > 4 && dim <= 512) {
+    // prompt portions: 32 tokens at a time
+    const int per = (dim + kChunkWarps - 1) / kChunkWarps;
+    const dim3 grid(B, heads, (vdim + 31) / 32);
+    const size_t smem = ((size_t)kChunk * (dim + 1) + (size_t)kChunk * dim + kChunk * 32 + kChunk * 33 + kChunkWarps * kChunk * 32 + kChunk + 1) *
+                        sizeof(float);
+    cudaError_t ce;
+    if (per <= 8) ce = launch_chunk<8>(ctx, a, grid, smem, nvc_stream(stream));
+    else if (per <= 16) ce = launch_chunk<16>(ctx, a, grid, smem, nvc_stream(stream));
+    else if (per <= 32) ce = launch_chunk<32>(ctx, a, grid, smem, nvc_stream(stream));
+    else if (per <= 64) ce = launch_chunk<64>(ctx, a, grid, smem, nvc_stream(stream));
+    else ce = launch_chunk<128>(ctx, a, grid, smem, nvc_stream(stream));
+    NVC_CUDA_CHECK(ctx, ce);
+    ctx->launches++;
+    return NVC_OK;
+  }
   const int dpt = dim <= 16 ? 16 : (dim <= 32 ? 32 : (dim <= 64 ? 64 : 128));
   const int groups = (dim + dpt - 1) / dpt;
   const dim3 grid(B, heads, (vdim + 31) / 32), block(32 * groups);

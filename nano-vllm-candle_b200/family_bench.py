@@ -1,4 +1,4 @@
-"""Karuzen beside the closest existing family (Qwen3, dense GQA) at equal layer sizes: prefill and decode throughput
+"""Karuzen or Ranilix beside the closest existing family (Qwen3, dense GQA) at equal layer sizes: prefill and decode throughput
 through LLMEngine, plus per-op times and roofline fractions.  Random weights, synthetic prompts.  Used by
 `bench.py --compare-families`; the default benchmark does not touch this module.
 
@@ -80,6 +80,120 @@ def karuzen_weights(cfg: dict, seed: int = 0):
             yield p + "mlp.shared.sg", mat(1, W)
 
 
+# ---- Ranilix at the same sizes: layers alternate between the windowed attention mixer (as many heads as the Qwen3 layer, 8 key /
+# value heads of 128) and the parallel mixer (half the heads as causal attention, half as retention heads of key size 64), a
+# squared-relu feed-forward of 1.5 ff (two matrices: the parameter count of the gated one with three)
+R_WINDOW, R_DIM, R_RET_DIM = 256, 128, 64
+
+
+def ranilix_config(sz: dict) -> dict:
+    H, W = sz["heads"], sz["width"]
+    att = {"heads": H, "kv_heads": 8, "dim": R_DIM, "vdim": R_DIM, "scale": R_DIM ** -0.5, "mask": {"size": R_WINDOW},
+           "rot": {"dims": 64, "base": 500000.0}, "v_mix": True}
+    par = {"left": {"heads": H // 2, "kv_heads": 4, "dim": R_DIM, "vdim": R_DIM, "scale": R_DIM ** -0.5, "rot": {"dims": 64, "base": 1000000.0}},
+           "left_scale": 1.0,
+           "right": {"heads": H // 2, "dim": R_RET_DIM, "vdim": R_DIM, "rot": {"dims": R_RET_DIM, "base": 1000000.0},
+                     "decay": [1.0 - 2.0 ** (-5 - 5 * i / max(1, H // 2 - 1)) for i in range(H // 2)]},
+           "right_scale": 1.0}
+    mlp = {"kind": "dense", "ff": sz["ff"] * 3 // 2}
+    layers = [{"type": "attention" if i % 2 == 0 else "parallel", "mixer": dict(att if i % 2 == 0 else par), "mlp": dict(mlp)}
+              for i in range(sz["layers"])]
+    return {"architecture": "Ranilix", "vocab": sz["vocab"], "width": W, "norm": {"eps": 1e-5}, "embedding": {"scale": W ** 0.5}, "layers": layers}
+
+
+def ranilix_weights(cfg: dict, seed: int = 0):
+    """(name, bf16 CPU tensor) pairs, generated one at a time."""
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    W = cfg["width"]
+
+    def mat(o, i):
+        return (torch.randn(o, i, generator=g) * i ** -0.5).bfloat16()
+
+    yield "embed", (torch.randn(cfg["vocab"], W, generator=g) * W ** -0.5).bfloat16()
+    yield "head", mat(cfg["vocab"], W)
+    yield "final.norm", torch.ones(W).bfloat16()
+    for i, ly in enumerate(cfg["layers"]):
+        m, p = ly["mixer"], f"l{i}."
+        yield p + "norm1", torch.ones(W).bfloat16()
+        yield p + "norm2", torch.ones(W).bfloat16()
+        if ly["type"] == "attention":
+            H, G, d, vd = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            for n, rows in (("q", H * d), ("k", G * d), ("v", G * vd)):
+                yield p + "mix." + n, mat(rows, W)
+                yield p + "mix." + n + ".b", torch.zeros(rows).bfloat16()
+            yield p + "mix.q.norm", torch.ones(d).bfloat16()
+            yield p + "mix.k.norm", torch.ones(d).bfloat16()
+            yield p + "mix.vmix", torch.tensor(0.3).bfloat16()
+            yield p + "mix.sink", torch.zeros(H).bfloat16()
+            yield p + "mix.g", mat(H * vd, W)
+            yield p + "mix.o", mat(W, H * vd)
+        else:
+            L, R = m["left"], m["right"]
+            yield p + "mix.left.q", mat(L["heads"] * L["dim"], W)
+            yield p + "mix.left.k", mat(L["kv_heads"] * L["dim"], W)
+            yield p + "mix.left.v", mat(L["kv_heads"] * L["vdim"], W)
+            yield p + "mix.left.o", mat(W, L["heads"] * L["vdim"])
+            yield p + "mix.right.q", mat(R["heads"] * R["dim"], W)
+            yield p + "mix.right.k", mat(R["heads"] * R["dim"], W)
+            yield p + "mix.right.v", mat(R["heads"] * R["vdim"], W)
+            yield p + "mix.right.g", mat(R["heads"] * R["vdim"], W)
+            yield p + "mix.right.o", mat(W, R["heads"] * R["vdim"])
+        yield p + "mlp.up", mat(ly["mlp"]["ff"], W)
+        yield p + "mlp.down", mat(W, ly["mlp"]["ff"])
+
+
+def ranilix_rooflines(cfg, prof: Dict[str, float], N: int, B: int, ctx_lens: List[int], q_lens: List[int], pk) -> dict:
+    """Per-op roofline of one profiled step: the times are sums over the layers, the work is summed the same way.  The
+    retention scan runs on the fp32 FMA pipe (its state is fp32): its fraction is against that pipe's peak (pk["fp32"])."""
+    W = cfg["width"]
+    work = {k: [0.0, 0.0] for k in ("gemm_in", "gemm_o", "gemm_up", "gemm_down", "attention", "retention_scan")}
+
+    def add(name, flops, nbytes):
+        work[name][0] += flops
+        work[name][1] += nbytes
+
+    def attn(a, window):
+        H, G, d, vd = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+        pairs, keys = 0, 0
+        for q, c in zip(q_lens, ctx_lens):
+            for t in range(c - q, c):
+                pairs += min(t + 1, window) if window else t + 1
+            keys += min(c, q + window - 1) if window else c
+        add("attention", 2.0 * pairs * H * (d + vd), 2.0 * (keys * G * (d + vd) + N * H * (d + vd)))
+
+    for ly in cfg["layers"]:
+        m, ff = ly["mixer"], ly["mlp"]["ff"]
+        if ly["type"] == "attention":
+            H, G, d, vd = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            n_in, n_o = H * d + G * d + G * vd + H * vd, H * vd
+            attn(m, m["mask"]["size"])
+        else:
+            L, R = m["left"], m["right"]
+            n_in = L["heads"] * L["dim"] + L["kv_heads"] * (L["dim"] + L["vdim"]) + R["heads"] * (2 * R["dim"] + 2 * R["vdim"])
+            n_o = L["heads"] * L["vdim"] + R["heads"] * R["vdim"]
+            attn(L, 0)
+            add("retention_scan", 4.0 * N * R["heads"] * R["dim"] * R["vdim"],
+                4.0 * (N * R["heads"] * (2 * R["dim"] + 2 * R["vdim"]) + 2 * B * R["heads"] * R["dim"] * R["vdim"]))
+        add("gemm_in", 2.0 * N * n_in * W, 2.0 * n_in * W + 2.0 * N * W + 4.0 * N * n_in)
+        add("gemm_o", 2.0 * N * n_o * W, 2.0 * n_o * W + 2.0 * N * n_o + 4.0 * N * W)
+        add("gemm_up", 2.0 * N * ff * W, 2.0 * (ff * W + N * (ff + W)))
+        add("gemm_down", 2.0 * N * ff * W, 2.0 * (ff * W + N * ff) + 4.0 * N * W)
+    out = {}
+    for name, (fl, by) in work.items():
+        if name in prof and fl > 0:
+            if name == "retention_scan":
+                tmin = max(fl / (pk.get("fp32", 70.0) * 1e12), by / (pk["hbm"] * 1e9)) * 1e6
+                out[name] = {"us": round(prof[name], 2), "fp32_tflops": round(fl / prof[name] / 1e6, 2), "gbs": round(by / prof[name] / 1e3, 1),
+                             "roofline_frac": round(tmin / prof[name], 3)}
+            else:
+                out[name] = _roof(fl, by, prof[name], pk)
+    for name in ("rms_norm_pair", "qkv_prep", "retention_prep", "retention_gate", "embed", "final_norm", "lm_head"):
+        if name in prof:
+            out[name] = {"us": round(prof[name], 2)}
+    return out
+
+
 def _prompts(n, length, vocab, seed):
     rng = np.random.default_rng(seed)
     return [rng.integers(0, vocab, length).tolist() for _ in range(n)]
@@ -151,21 +265,25 @@ def karuzen_rooflines(cfg, prof: Dict[str, float], N: int, B: int, ctx_lens: Lis
     return out
 
 
-def compare(ctx_ours, sizes=None, batch_p=16, batch_d=64, plen=512, K=32, W=4, peaks=None) -> dict:
+def compare(ctx_ours, sizes=None, batch_p=16, batch_d=64, plen=512, K=32, W=4, peaks=None, family="karuzen") -> dict:
     import importlib
     import torch
     eng = importlib.import_module("nano-vllm-candle_b200.engine")
     synth = importlib.import_module("nano-vllm-candle_b200.synth")
     pk = peaks or {"bf16": 1590.0, "hbm": 6650.0, "source": "fallback"}
+    make_config, make_weights, rooflines = {"karuzen": (karuzen_config, karuzen_weights, karuzen_rooflines),
+                                            "ranilix": (ranilix_config, ranilix_weights, ranilix_rooflines)}[family]
     T = batch_p * plen
     nblocks = max(batch_p, batch_d) * (-(-(plen + W + K + 24) // BLOCK)) + 8
     results = []
     for sz in sizes or SIZES:
         rec = {"size": sz["name"]}
-        # ---- Karuzen
-        cfg = karuzen_config(sz)
+        if family == "ranilix" and "moe" in sz:
+            continue                                               # the design has no mixture of experts
+        # ---- the registry family
+        cfg = make_config(sz)
         t0 = time.perf_counter()
-        kr = eng.ModelRunner.from_config(ctx_ours, cfg, karuzen_weights(cfg), num_kvcache_blocks=nblocks, kvcache_block_size=BLOCK,
+        kr = eng.ModelRunner.from_config(ctx_ours, cfg, make_weights(cfg), num_kvcache_blocks=nblocks, kvcache_block_size=BLOCK,
                                          max_num_seqs=max(batch_p, batch_d), max_num_batched_tokens=T,
                                          max_model_len=(-(-(plen + W + K + 24) // BLOCK)) * BLOCK)
         load_s = time.perf_counter() - t0
@@ -174,7 +292,7 @@ def compare(ctx_ours, sizes=None, batch_p=16, batch_d=64, plen=512, K=32, W=4, p
         engine.step()                                              # one more decode step, un-captured, with events
         prof_d = kr.profile()
         ctx_d = plen + max(W, 3) + 2
-        roof_d = karuzen_rooflines(cfg, prof_d, batch_d, batch_d, [ctx_d] * batch_d, [1] * batch_d, pk)
+        roof_d = rooflines(cfg, prof_d, batch_d, batch_d, [ctx_d] * batch_d, [1] * batch_d, pk)
         engine.close()
         e2 = eng.LLMEngine(eng.Scheduler(eng.SchedulerConfig(batch_p, T, -1, nblocks, BLOCK)), kr, greedy=True)
         for p in _prompts(batch_p, plen, sz["vocab"], 77):
@@ -182,9 +300,9 @@ def compare(ctx_ours, sizes=None, batch_p=16, batch_d=64, plen=512, K=32, W=4, p
         kr.arm_profile()
         e2.step()
         prof_p = kr.profile()
-        roof_p = karuzen_rooflines(cfg, prof_p, T, batch_p, [plen] * batch_p, [plen] * batch_p, pk)
+        roof_p = rooflines(cfg, prof_p, T, batch_p, [plen] * batch_p, [plen] * batch_p, pk)
         e2.close()
-        rec["karuzen"] = {"prefill_tok_s": round(p_tps), "decode_tok_s": round(d_tps), "decode_ms_per_step": round(ms_step, 4),
+        rec[family] = {"prefill_tok_s": round(p_tps), "decode_tok_s": round(d_tps), "decode_ms_per_step": round(ms_step, 4),
                           "kernels_per_decode_step": launches, "weights_load_s": round(load_s, 1),
                           "weight_bytes": kr.weight_bytes(), "cache_bytes_per_token": kr.kv_bytes_per_token(),
                           "prefill_ops": roof_p, "decode_ops": roof_d}
@@ -217,7 +335,7 @@ def compare(ctx_ours, sizes=None, batch_p=16, batch_d=64, plen=512, K=32, W=4, p
         qr_.close()
         torch.cuda.empty_cache()
         results.append(rec)
-    return {"metric": "karuzen_vs_qwen3_equal_layer_sizes", "unit": "tok/s", "dtype": "bf16", "data": "synthetic",
+    return {"metric": family + "_vs_qwen3_equal_layer_sizes", "unit": "tok/s", "dtype": "bf16", "data": "synthetic",
             "workload": {"prefill": f"{batch_p} x {plen} tokens in one step", "decode": f"batch {batch_d} at context ~{plen + W + K}",
                          "timing": "prefill: host wall clock around the synchronous engine step, best of 3 after a warm-up; decode: CUDA events "
                                    "around K replays of the captured step; per-op: CUDA events inside one un-captured step"},

@@ -558,10 +558,10 @@ def attn_paged_wide(ctx, q, k_cache, v_cache, block_tables, context_lens, cu_seq
     return out
 
 
-def retention_scan(ctx, q, k, v, state, state_slots, cu_seqlens, positions, decay, heads: int, dim: int, vdim: int):
+def retention_scan(ctx, q, k, v, state, state_slots, cu_seqlens, positions, decay, heads: int, dim: int, vdim: int, max_qlen: int = 1 << 20):
     """q, k: fp32 [N, heads * dim]; v: fp32 [N, heads * vdim]; state: fp32 [slots, heads, dim, vdim], updated in place."""
     o = torch.empty(q.shape[0], heads * vdim, dtype=torch.float32, device=q.device)
     check(ctx.l.nvc_retention_scan(ctx.h, _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(o), o.stride(0), _ptr(state),
-                                   _ptr(state_slots), _ptr(cu_seqlens), _ptr(positions), _ptr(decay), state_slots.numel(), heads, dim, vdim,
+                                   _ptr(state_slots), _ptr(cu_seqlens), _ptr(positions), _ptr(decay), state_slots.numel(), max_qlen, heads, dim, vdim,
                                    _stream()), "nvc_retention_scan", ctx.h)
     return o

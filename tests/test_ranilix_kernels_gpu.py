@@ -278,22 +278,24 @@ def plain_retention(q, k, v, decay, S):
     return o, S
 
 
-@pytest.mark.parametrize("H,d,vd", [(3, 16, 24), (2, 32, 64), (1, 8, 1), (4, 64, 40), (2, 128, 96), (2, 200, 72)])
-def test_retention_carries_state_between_portions_and_slots(ctx, ops, H, d, vd):
+@pytest.mark.parametrize("form", ["token by token", "32 tokens at a time"])
+@pytest.mark.parametrize("H,d,vd", [(3, 16, 24), (2, 32, 64), (1, 8, 1), (4, 64, 40), (2, 128, 96), (2, 200, 72), (1, 300, 33)])
+def test_retention_carries_state_between_portions_and_slots(ctx, ops, H, d, vd, form):
+    max_qlen = 1 if form == "token by token" else 64
     g = torch.Generator().manual_seed(14)
     slots = 4
-    decay = torch.tensor([0.5, 0.9, 0.99, 0.999])[:H].contiguous()
+    decay = torch.tensor([0.5, 1.0, 0.99, 0.0])[:H].contiguous()
     state = torch.randn(slots, H, d, vd, generator=g)        # whatever an earlier owner left behind
     state_d = state.to(DEV)
     ref = {}
-    lens = {"a": 37, "b": 5, "c": 64}
+    lens = {"a": 37, "b": 5, "c": 97}
     data = {n: (torch.randn(T, H, d, generator=g), torch.randn(T, H, d, generator=g) * d ** -0.5, torch.randn(T, H, vd, generator=g)) for n, T in lens.items()}
     want = {n: plain_retention(*data[n], decay, torch.zeros(H, d, vd))[0] for n in lens}
     got = {n: torch.zeros(T, H * vd) for n, T in lens.items()}
     at = {n: 0 for n in lens}
     slot_of = {"a": 2, "b": 0, "c": 3}
     # steps of (name, count): portions beside single tokens, in changing batch order
-    sched = [[("a", 20), ("b", 1)], [("b", 1), ("a", 1), ("c", 33)], [("c", 1), ("b", 3), ("a", 16)], [("c", 30)]]
+    sched = [[("a", 20), ("b", 1)], [("b", 1), ("a", 1), ("c", 33)], [("c", 1), ("b", 3), ("a", 16)], [("c", 63)]]
     for step in sched:
         cu, pos, q, k, v = [0], [], [], [], []
         for n, c in step:
@@ -303,7 +305,7 @@ def test_retention_carries_state_between_portions_and_slots(ctx, ops, H, d, vd):
             cu.append(cu[-1] + c)
         N = cu[-1]
         o = ops.retention_scan(ctx, torch.cat(q).reshape(N, H * d).to(DEV), torch.cat(k).reshape(N, H * d).to(DEV), torch.cat(v).reshape(N, H * vd).to(DEV),
-                               state_d, i32([slot_of[n] for n, _ in step]), i32(cu), i32(pos), decay.to(DEV), H, d, vd).cpu()
+                               state_d, i32([slot_of[n] for n, _ in step]), i32(cu), i32(pos), decay.to(DEV), H, d, vd, max_qlen).cpu()
         for b, (n, c) in enumerate(step):
             got[n][at[n]:at[n] + c] = o[cu[b]:cu[b + 1]]
             at[n] += c
@@ -330,8 +332,9 @@ def test_retention_remembers_a_far_token_by_its_decay(ctx, ops):
     k[3, :, :] = 0.0
     k[3, :, 0] = 1.0           # token 3 writes along axis 0
     q[T - 1, :, 0] = 1.0       # the last token reads axis 0
-    state = torch.zeros(1, H, d, vd, device=DEV)
-    o = ops.retention_scan(ctx, q.reshape(T, -1).to(DEV), k.reshape(T, -1).to(DEV), v.reshape(T, -1).to(DEV), state, i32([0]), i32([0, T]),
-                           i32(list(range(T))), decay.to(DEV), H, d, vd).cpu().view(T, H, vd)
-    for h in range(H):
-        assert torch.allclose(o[T - 1, h], float(decay[h]) ** (T - 1 - 3) * v[3, h], rtol=1e-4, atol=1e-6)
+    for max_qlen in (1, T):
+        state = torch.zeros(1, H, d, vd, device=DEV)
+        o = ops.retention_scan(ctx, q.reshape(T, -1).to(DEV), k.reshape(T, -1).to(DEV), v.reshape(T, -1).to(DEV), state, i32([0]), i32([0, T]),
+                               i32(list(range(T))), decay.to(DEV), H, d, vd, max_qlen).cpu().view(T, H, vd)
+        for h in range(H):
+            assert torch.allclose(o[T - 1, h], float(decay[h]) ** (T - 1 - 3) * v[3, h], rtol=1e-4, atol=1e-6)
