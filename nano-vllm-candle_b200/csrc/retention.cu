@@ -100,21 +100,33 @@ __global__ void retention_scan_kernel(const RetArgs a) {
 constexpr int kChunk = 32;          // tokens per chunk
 constexpr int kChunkWarps = 4;
 
+__device__ __forceinline__ float dot4(const float4& x, const float4& y, float acc) {
+  acc = fmaf(x.x, y.x, acc);
+  acc = fmaf(x.y, y.y, acc);
+  acc = fmaf(x.z, y.z, acc);
+  return fmaf(x.w, y.w, acc);
+}
+
+// float4 units per staged q row: odd, so that the 8 lanes of a 128-bit shared-memory phase (lane = token) hit distinct banks
+__host__ __device__ inline int chunk_q_stride4(int dim) { const int q4 = (dim + 3) / 4; return (q4 & 1) ? q4 : q4 + 1; }
+
+// Shared-memory operands are read as float4 (one load per four FMAs) and reused across a register tile: the kernel is bound
+// by the FMA pipe, not by shared-memory loads.
 template <int DPT>
 __global__ void __launch_bounds__(kChunkWarps * 32) retention_chunk_kernel(const RetArgs a) {
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   pdl_trigger();
   const int b = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * 32;
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const int v = v0 + lane;
   const bool vok = v < a.vdim;
-  const int dim = a.dim, qs = dim + 1;                 // row stride of the staged q (lane = token: conflict-free)
-  float* q_s = sm;                                     // [32][dim + 1]
-  float* k_s = q_s + kChunk * qs;                      // [32][dim]   (read as broadcasts)
-  float* v_s = k_s + kChunk * dim;                     // [32][32]
-  float* a_s = v_s + kChunk * 32;                      // [32][33]
-  float* part = a_s + kChunk * 33;                     // [warps][32][32]
-  float* gp = part + kChunkWarps * kChunk * 32;        // decay^0 .. decay^32
+  const int dim = a.dim, q4 = (dim + 3) / 4, dim4 = 4 * q4, RS = chunk_q_stride4(dim);
+  float4* q_s = reinterpret_cast<float4*>(sm);                 // [32][RS]   rows padded with zeros
+  float4* k_s = q_s + kChunk * RS;                             // [32][q4]   (read as broadcasts)
+  float* v_s = reinterpret_cast<float*>(k_s + kChunk * q4);    // [32][32]
+  float4* a_s = reinterpret_cast<float4*>(v_s + kChunk * 32);  // [32][9]    A[t][j], j in fours, zero above the diagonal
+  float* part = reinterpret_cast<float*>(a_s + kChunk * 9);    // [warps][32][32]
+  float* gp = part + kChunkWarps * kChunk * 32;                // decay^0 .. decay^32
   const float dec = __ldg(a.decay + h);
   if (threadIdx.x == 0) {
     float p = 1.f;
@@ -123,59 +135,92 @@ __global__ void __launch_bounds__(kChunkWarps * 32) retention_chunk_kernel(const
   pdl_wait();
   const int r0 = a.cu_seqlens ? a.cu_seqlens[b] : b;
   const int r1 = a.cu_seqlens ? a.cu_seqlens[b + 1] : b + 1;
-  const int d0 = w * DPT;
+  const int d0 = w * DPT;                                      // this warp's rows of the state (DPT is a multiple of 4)
   float S[DPT];
   float* sp = a.state + (((int64_t)a.state_slots[b] * a.heads + h) * dim) * a.vdim;
   const bool fresh = a.positions[r0] == 0;
 #pragma unroll
   for (int i = 0; i < DPT; ++i) S[i] = (!fresh && vok && d0 + i < dim) ? sp[(int64_t)(d0 + i) * a.vdim + v] : 0.f;
+  float* q_sf = reinterpret_cast<float*>(q_s);
+  float* k_sf = reinterpret_cast<float*>(k_s);
   for (int c0 = r0; c0 < r1; c0 += kChunk) {
     const int n = min(kChunk, r1 - c0);
     __syncthreads();                                   // the previous chunk is done with the staged rows
-    for (int idx = threadIdx.x; idx < kChunk * dim; idx += blockDim.x) {
-      const int t = idx / dim, d = idx - t * dim;
-      const bool in = t < n;
-      q_s[t * qs + d] = in ? a.q[(int64_t)(c0 + t) * a.ldq + h * dim + d] : 0.f;
-      k_s[t * dim + d] = in ? a.k[(int64_t)(c0 + t) * a.ldk + h * dim + d] : 0.f;
+    for (int idx = threadIdx.x; idx < kChunk * dim4; idx += blockDim.x) {
+      const int t = idx / dim4, d = idx - t * dim4;
+      const bool in = t < n && d < dim;
+      q_sf[t * 4 * RS + d] = in ? a.q[(int64_t)(c0 + t) * a.ldq + h * dim + d] : 0.f;
+      k_sf[t * dim4 + d] = in ? a.k[(int64_t)(c0 + t) * a.ldk + h * dim + d] : 0.f;
     }
     for (int idx = threadIdx.x; idx < kChunk * 32; idx += blockDim.x) {
       const int t = idx >> 5, c = idx & 31;
       v_s[idx] = (t < n && v0 + c < a.vdim) ? a.v[(int64_t)(c0 + t) * a.ldv + h * a.vdim + v0 + c] : 0.f;
     }
     __syncthreads();
-    // ---- A[t][j]: lane = t, this warp's j = w, w + 4, ...
+    // ---- A[t][j]: lane = t; warp w takes the groups of four keys jg = w and w + 4 (j = 4 jg + u)
     {
-      float acc[kChunk / kChunkWarps];
+      float acc[2][4];
 #pragma unroll
-      for (int jj = 0; jj < kChunk / kChunkWarps; ++jj) acc[jj] = 0.f;
-      for (int d = 0; d < dim; ++d) {
-        const float qv = q_s[lane * qs + d];
+      for (int g = 0; g < 2; ++g) acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
+      for (int d4 = 0; d4 < q4; ++d4) {
+        const float4 qv = q_s[lane * RS + d4];
 #pragma unroll
-        for (int jj = 0; jj < kChunk / kChunkWarps; ++jj) acc[jj] = fmaf(qv, k_s[(w + jj * kChunkWarps) * dim + d], acc[jj]);
+        for (int g = 0; g < 2; ++g)
+#pragma unroll
+          for (int u = 0; u < 4; ++u) acc[g][u] = dot4(qv, k_s[(4 * (w + 4 * g) + u) * q4 + d4], acc[g][u]);
       }
 #pragma unroll
-      for (int jj = 0; jj < kChunk / kChunkWarps; ++jj) {
-        const int j = w + jj * kChunkWarps;
-        a_s[lane * 33 + j] = j <= lane ? acc[jj] * gp[lane - j] : 0.f;
+      for (int g = 0; g < 2; ++g) {
+        const int j0 = 4 * (w + 4 * g);
+        float4 r;
+        r.x = j0 <= lane ? acc[g][0] * gp[lane - j0] : 0.f;
+        r.y = j0 + 1 <= lane ? acc[g][1] * gp[lane - j0 - 1] : 0.f;
+        r.z = j0 + 2 <= lane ? acc[g][2] * gp[lane - j0 - 2] : 0.f;
+        r.w = j0 + 3 <= lane ? acc[g][3] * gp[lane - j0 - 3] : 0.f;
+        a_s[lane * 9 + w + 4 * g] = r;
       }
     }
     // ---- the state's share of every output: this warp's rows of S against q_t, lane = value column
     for (int t = 0; t < n; ++t) {
       float acc = 0.f;
 #pragma unroll
-      for (int i = 0; i < DPT; ++i)
-        if (d0 + i < dim) acc = fmaf(S[i], q_s[t * qs + d0 + i], acc);
+      for (int i4 = 0; i4 < DPT / 4; ++i4) {
+        if (d0 + 4 * i4 < dim4) {
+          const float4 qv = q_s[t * RS + (d0 >> 2) + i4];
+          acc = fmaf(S[4 * i4], qv.x, acc);
+          acc = fmaf(S[4 * i4 + 1], qv.y, acc);
+          acc = fmaf(S[4 * i4 + 2], qv.z, acc);
+          acc = fmaf(S[4 * i4 + 3], qv.w, acc);
+        }
+      }
       part[(w * kChunk + t) * 32 + lane] = acc;
     }
     __syncthreads();
-    // ---- o_t for this warp's tokens t = w, w + 4, ...
-    for (int t = w; t < n; t += kChunkWarps) {
-      float acc = 0.f;
-      for (int j = 0; j <= t; ++j) acc = fmaf(a_s[t * 33 + j], v_s[j * 32 + lane], acc);
-      float cross = 0.f;
+    // ---- o_t for this warp's tokens t = w, w + 4, ... (a register tile of 8 tokens against four value rows at a time)
+    {
+      float acc[kChunk / kChunkWarps];
 #pragma unroll
-      for (int g = 0; g < kChunkWarps; ++g) cross += part[(g * kChunk + t) * 32 + lane];
-      if (vok) a.o[(int64_t)(c0 + t) * a.ldo + h * a.vdim + v] = fmaf(gp[t + 1], cross, acc);
+      for (int tt = 0; tt < kChunk / kChunkWarps; ++tt) acc[tt] = 0.f;
+      const int j4n = (n + 3) >> 2;
+      for (int j4 = 0; j4 < j4n; ++j4) {
+        float4 vv;
+        vv.x = v_s[(4 * j4) * 32 + lane];
+        vv.y = v_s[(4 * j4 + 1) * 32 + lane];
+        vv.z = v_s[(4 * j4 + 2) * 32 + lane];
+        vv.w = v_s[(4 * j4 + 3) * 32 + lane];
+#pragma unroll
+        for (int tt = 0; tt < kChunk / kChunkWarps; ++tt) acc[tt] = dot4(a_s[(w + kChunkWarps * tt) * 9 + j4], vv, acc[tt]);
+      }
+#pragma unroll
+      for (int tt = 0; tt < kChunk / kChunkWarps; ++tt) {
+        const int t = w + kChunkWarps * tt;
+        if (t < n) {
+          float cross = 0.f;
+#pragma unroll
+          for (int g = 0; g < kChunkWarps; ++g) cross += part[(g * kChunk + t) * 32 + lane];
+          if (vok) a.o[(int64_t)(c0 + t) * a.ldo + h * a.vdim + v] = fmaf(gp[t + 1], cross, acc[tt]);
+        }
+      }
     }
     // ---- the state after the chunk
     {
@@ -185,8 +230,15 @@ __global__ void __launch_bounds__(kChunkWarps * 32) retention_chunk_kernel(const
       for (int j = 0; j < n; ++j) {
         const float vv = v_s[j * 32 + lane] * gp[n - 1 - j];
 #pragma unroll
-        for (int i = 0; i < DPT; ++i)
-          if (d0 + i < dim) S[i] = fmaf(k_s[j * dim + d0 + i], vv, S[i]);
+        for (int i4 = 0; i4 < DPT / 4; ++i4) {
+          if (d0 + 4 * i4 < dim4) {
+            const float4 kv = k_s[j * q4 + (d0 >> 2) + i4];
+            S[4 * i4] = fmaf(kv.x, vv, S[4 * i4]);
+            S[4 * i4 + 1] = fmaf(kv.y, vv, S[4 * i4 + 1]);
+            S[4 * i4 + 2] = fmaf(kv.z, vv, S[4 * i4 + 2]);
+            S[4 * i4 + 3] = fmaf(kv.w, vv, S[4 * i4 + 3]);
+          }
+        }
       }
     }
   }
@@ -218,10 +270,10 @@ extern "C" int nvc_retention_scan(nvc_ctx* ctx, const float* q, int ldq, const f
   RetArgs a{q, k, v, o, ldq, ldk, ldv, ldo, state, state_slots, cu_seqlens, positions, decay, heads, dim, vdim};
   if (cu_seqlens && max_qlen > 4 && dim <= 512) {
     // prompt portions: 32 tokens at a time
-    const int per = (dim + kChunkWarps - 1) / kChunkWarps;
+    const int per = ((dim + 3) / 4 * 4 + kChunkWarps - 1) / kChunkWarps;     // rows of the state per warp
     const dim3 grid(B, heads, (vdim + 31) / 32);
-    const size_t smem = ((size_t)kChunk * (dim + 1) + (size_t)kChunk * dim + kChunk * 32 + kChunk * 33 + kChunkWarps * kChunk * 32 + kChunk + 1) *
-                        sizeof(float);
+    const size_t smem = ((size_t)kChunk * 4 * chunk_q_stride4(dim) + (size_t)kChunk * 4 * ((dim + 3) / 4) + kChunk * 32 + kChunk * 36 +
+                         kChunkWarps * kChunk * 32 + kChunk + 4) * sizeof(float);
     cudaError_t ce;
     if (per <= 8) ce = launch_chunk<8>(ctx, a, grid, smem, nvc_stream(stream));
     else if (per <= 16) ce = launch_chunk<16>(ctx, a, grid, smem, nvc_stream(stream));
