@@ -270,6 +270,11 @@ int nvc_engine_step_inputs(const nvc_engine* e, const int32_t** ids, const int32
 /* Chunked mode: emit[b] != 0 when sequence b of the last schedule ends its pending tokens in this
  * step and takes the sampled token (always 1 without chunked prefill). */
 int nvc_engine_step_emit_mask(const nvc_engine* e, const int32_t** emit);
+/* Models with recurrent state: slots[b] = the state slot of sequence b of the last schedule (what a caller who runs the
+ * model itself passes to nvc_runner_set_state_slots); -1 for every sequence when the model keeps none.  Such a caller runs
+ * every scheduled batch exactly once before nvc_engine_post_process: writing the cache twice is harmless, feeding a
+ * recurrence the same tokens twice is not. */
+int nvc_engine_step_state_slots(const nvc_engine* e, const int32_t** slots);
 /* Scheduler::post_process (:213-249) for the batch of the last schedule. */
 int nvc_engine_post_process(nvc_engine* e, const int32_t* token_ids, int n);
 /* LLMEngine::step (:239-264): schedule -> runner -> post_process. */

@@ -83,6 +83,7 @@ def declare(l: C.CDLL) -> None:
         "nvc_engine_schedule": [_vp, C.POINTER(ScheduleInfoC)],
         "nvc_engine_step_inputs": [_vp] + [C.POINTER(_pi32)] * 6 + [C.POINTER(C.POINTER(C.c_int64))],
         "nvc_engine_step_emit_mask": [_vp, C.POINTER(_pi32)],
+        "nvc_engine_step_state_slots": [_vp, C.POINTER(_pi32)],
         "nvc_engine_post_process": [_vp, _vp, _i],
         "nvc_engine_step": [_vp, C.POINTER(StepOutputC)],
         "nvc_engine_is_finished": [_vp],

@@ -456,6 +456,7 @@ struct nvc_engine {
   std::vector<int32_t> q_lens, emit;           // per sequence of the batch
   std::vector<int32_t> ids, positions, cu_seqlens, slot_mapping, block_tables, context_lens, out_tokens;
   std::vector<int64_t> seq_ids;
+  std::vector<int32_t> state_slots;            // per sequence of the batch (-1 when the model keeps no recurrent state)
   int max_blocks = 0, max_seqlen = 0;
   bool sampling = false;                       // on-device temperature sampling
   uint64_t sampling_seed = 0;
@@ -484,6 +485,8 @@ void build_inputs(nvc_engine* e) {
   e->block_tables.clear(); e->context_lens.clear(); e->seq_ids.clear();
   e->max_blocks = 0; e->max_seqlen = 0;
   for (auto& s : e->batch) e->seq_ids.push_back(s->seq_id);
+  e->state_slots.clear();
+  for (auto& s : e->batch) e->state_slots.push_back(s->state_slot);
   if (e->chunked) {
     // tokens [num_computed, num_computed + q) of every sequence; slot of token t = N1's rule per token:
     // block_table[t / BS] * BS + t % BS
@@ -581,9 +584,7 @@ int arm_sampling(nvc_engine* e) {
 // models with recurrent state: tell the runner which state slot every sequence of the batch owns
 int arm_state_slots(nvc_engine* e) {
   if (!e->runner || e->scheduler.block_manager.num_state_slots == 0) return NVC_OK;
-  std::vector<int32_t> slots;
-  for (auto& s : e->batch) slots.push_back(s->state_slot);
-  return nvc_runner_set_state_slots(e->runner, slots.data(), (int)slots.size());
+  return nvc_runner_set_state_slots(e->runner, e->state_slots.data(), (int)e->state_slots.size());
 }
 
 void rollback_failed_step(nvc_engine* e) {
@@ -723,6 +724,13 @@ int nvc_engine_step_emit_mask(const nvc_engine* e, const int32_t** emit) {
   if (!e || !emit) return NVC_EINVAL;
   if (!e->batch_valid) return NVC_ESTATE;
   *emit = e->emit.data();
+  return NVC_OK;
+}
+
+int nvc_engine_step_state_slots(const nvc_engine* e, const int32_t** slots) {
+  if (!e || !slots) return NVC_EINVAL;
+  if (!e->batch_valid) return NVC_ESTATE;
+  *slots = e->state_slots.data();
   return NVC_OK;
 }
 

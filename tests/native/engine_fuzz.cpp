@@ -7,6 +7,7 @@
 // DummyModelRunner (llm_engine.rs:20-33).  It also keeps a model of the paged KV cache (g_kv below).  Random valid and
 // invalid call sequences; any contract violation, sanitizer report or wrong output aborts.  test_native_asan.py also
 // builds it against deliberately broken copies of engine.cpp and requires a failure.
+#include <algorithm>
 #include <cctype>
 #include <cstdint>
 #include <cstdio>
@@ -22,6 +23,9 @@
 struct nvc_runner {
   int num_blocks, bs, max_seqs, budget, vocab;
   long prefill = 0, paged = 0, mixed = 0, decode = 0;
+  int state_slots = 0;                      // > 0: a model with per-sequence recurrent state
+  std::vector<int32_t> armed;               // slots named for the next step
+  long stateful = 0;
 };
 
 static std::string g_trace;   // configuration + calls of the current engine, printed when a check fails
@@ -43,6 +47,15 @@ static std::vector<std::pair<int32_t, int32_t>> g_kv;
 // failed in the runner wrote nothing).  nvc_engine_step must then roll its batch back (sequences re-queued, the
 // prefix-cache entries of their blocks dropped): otherwise a later step reads context that was never written and
 // the cache model below goes red.
+// Model of the recurrent state slots: a running hash of the tokens a slot's state has absorbed and how many.  A step
+// requires that every sequence which continues (first position > 0) finds in its slot exactly the hash of ITS OWN earlier
+// tokens (read back from the cache model through its block table): a slot handed to two sequences, lost at a
+// preemption or not reset at position 0 goes red here.
+static std::vector<std::pair<uint64_t, int32_t>> g_state;
+// false once a batch was scheduled but never run (the harness's bare `sched` noise): a cache write can be repeated, a
+// recurrence can not, so from then on only the slots' range and distinctness are checked for this engine
+static bool g_state_exact = true;
+static uint64_t state_fold(uint64_t h, int32_t tok) { return (h ^ (uint64_t)(uint32_t)tok) * 0x100000001b3ull + 0x9e3779b97f4a7c15ull; }
 static bool g_fail_next = false;
 static long g_injected = 0;
 #define MAYBE_FAIL()            \
@@ -53,6 +66,26 @@ static long g_injected = 0;
       return NVC_EINVAL;        \
     }                           \
   } while (0)
+
+static void state_step(const nvc_runner* r, const int32_t* armed, int B, const int32_t* ids, const int32_t* pos, const int32_t* cu,
+                       const int32_t* bt, int max_blocks) {
+  std::set<int32_t> taken;
+  for (int b = 0; b < B; ++b) {
+    const int32_t sl = armed[b];
+    REQUIRE(sl >= 0 && sl < r->state_slots && taken.insert(sl).second);
+    const int p0 = pos[cu[b]];
+    if (p0 == 0) {
+      g_state[sl] = {0, 0};
+    } else {
+      REQUIRE(bt);                                                   // a continuation reads its context through the table
+      uint64_t h = 0;
+      for (int p = 0; p < p0; ++p) h = state_fold(h, g_kv[(size_t)bt[(size_t)b * max_blocks + p / r->bs] * r->bs + p % r->bs].first);
+      if (g_state_exact) REQUIRE(g_state[sl].second == p0 && g_state[sl].first == h);
+    }
+    for (int i = cu[b]; i < cu[b + 1]; ++i) g_state[sl].first = state_fold(g_state[sl].first, ids[i]);
+    g_state[sl].second = p0 + (cu[b + 1] - cu[b]);
+  }
+}
 
 static void check_step(nvc_runner* r, const int32_t* ids, const int32_t* pos, const int32_t* cu, const int32_t* slots,
                        const int32_t* bt, int max_blocks, const int32_t* ctx, int num_decode, int B, int N, int max_seqlen,
@@ -84,6 +117,12 @@ static void check_step(nvc_runner* r, const int32_t* ids, const int32_t* pos, co
     }
     out[b] = (ids[cu[b + 1] - 1] + 1) % r->vocab;
   }
+  if (r->state_slots > 0) {
+    REQUIRE((int)r->armed.size() == B);                               // the engine named a slot for every sequence
+    state_step(r, r->armed.data(), B, ids, pos, cu, bt, max_blocks);
+    ++r->stateful;
+  }
+  r->armed.clear();
   for (int i = 0; i < N; ++i)
     if (slots[i] >= 0) g_kv[(size_t)slots[i]] = {ids[i], pos[i]};
   if (bt)
@@ -129,6 +168,8 @@ int nvc_runner_decode(nvc_runner* r, const int32_t* ids, const int32_t* position
   nvc_runner wide = *r;
   wide.budget = r->max_seqs;                                         // a decode step is bounded by max_num_seqs only
   check_step(&wide, ids, positions, cu.data(), slot_mapping, block_tables, max_blocks, context_lens, B, B, B, 1, out_tokens);
+  r->armed.clear();
+  r->stateful = wide.stateful;
   return 0;
 }
 int nvc_runner_set_sampling(nvc_runner*, const float* t, const uint64_t* s, int B, uint64_t) {
@@ -151,6 +192,12 @@ int nvc_runner_load_tensor(nvc_runner*, const char*, const void*, int, const int
 int nvc_runner_takes_raw_tensors(const nvc_runner*) { return 0; }
 int nvc_runner_needs_block_tables(const nvc_runner*) { return 0; }
 int nvc_runner_set_logit_rows(nvc_runner*, const int32_t*, int) { return 0; }
+int nvc_runner_num_state_slots(const nvc_runner* r) { return r->state_slots; }
+int nvc_runner_set_state_slots(nvc_runner* r, const int32_t* slots, int B) {
+  REQUIRE(r->state_slots > 0 && slots && B > 0 && B <= r->max_seqs);
+  r->armed.assign(slots, slots + B);
+  return 0;
+}
 }
 
 // Phase 2: the HF loader's JSON / safetensors readers on mutated files (argv[3] = scratch directory).
@@ -258,6 +305,10 @@ int main(int argc, char** argv) {
     cfg.enable_chunked_prefill = rng() % 2;
     nvc_runner runner{cfg.num_kvcache_blocks, cfg.kvcache_block_size, cfg.max_num_seqs, cfg.max_num_batched_tokens, 64};
     const bool with_runner = rng() % 4 != 0;
+    // every third runner keeps recurrent state: as many slots as sequences; the engine must refuse prefix caching for it
+    if (rng() % 3 == 0 && cfg.max_num_seqs > 0) runner.state_slots = cfg.max_num_seqs;
+    g_state.assign((size_t)std::max(runner.state_slots, 1), {0, -1});
+    g_state_exact = true;
     g_trace = "cfg seqs " + std::to_string(cfg.max_num_seqs) + " budget " + std::to_string(cfg.max_num_batched_tokens) +
               " eos " + std::to_string(cfg.eos) + " blocks " + std::to_string(cfg.num_kvcache_blocks) + " bs " +
               std::to_string(cfg.kvcache_block_size) + " prefix " + std::to_string(cfg.enable_prefix_caching) + " chunked " +
@@ -267,6 +318,7 @@ int main(int argc, char** argv) {
       REQUIRE(e == nullptr);
       continue;
     }
+    REQUIRE(!(with_runner && runner.state_slots > 0 && cfg.enable_prefix_caching));   // recurrent state can not skip a cached prefix
     ++created;
     g_kv.assign((size_t)cfg.num_kvcache_blocks * cfg.kvcache_block_size, {-1, -1});
     if (rng() % 3 == 0) nvc_engine_set_sampling(e, 1, rng());
@@ -326,6 +378,14 @@ int main(int argc, char** argv) {
               REQUIRE(writer[(size_t)blk] == -1 || writer[(size_t)blk] == b2);
               writer[(size_t)blk] = b2;
             }
+          }
+          if (with_runner && runner.state_slots > 0) {               // ... the recurrence included
+            const int32_t* ss;
+            REQUIRE(nvc_engine_step_state_slots(e, &ss) == 0);
+            if (op == 3) g_state_exact = false;                      // scheduled, never post-processed: it will be scheduled again
+            std::vector<int32_t> cu2((size_t)info.num_seqs + 1);
+            for (int b = 0; b <= info.num_seqs; ++b) cu2[(size_t)b] = info.is_prefill ? cu[b] : b;
+            state_step(&runner, ss, info.num_seqs, ids, pos, cu2.data(), bt, info.max_blocks);
           }
           if (with_runner)                                           // whoever scheduled is assumed to run the model
             for (int i = 0; i < nt; ++i)
@@ -410,8 +470,9 @@ int main(int argc, char** argv) {
     }
     REQUIRE(nvc_engine_destroy(e) == 0);
     totals.prefill += runner.prefill; totals.paged += runner.paged; totals.mixed += runner.mixed; totals.decode += runner.decode;
+    totals.stateful += runner.stateful;
   }
-  printf("ok engines %ld steps %ld verified outputs %ld views %ld injected %ld runner calls: prefill %ld paged %ld mixed %ld decode %ld\n",
-         created, steps_ok, finished, checked, g_injected, totals.prefill, totals.paged, totals.mixed, totals.decode);
+  printf("ok engines %ld steps %ld verified outputs %ld views %ld injected %ld runner calls: prefill %ld paged %ld mixed %ld decode %ld stateful %ld\n",
+         created, steps_ok, finished, checked, g_injected, totals.prefill, totals.paged, totals.mixed, totals.decode, totals.stateful);
   return 0;
 }

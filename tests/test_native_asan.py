@@ -37,10 +37,13 @@ def test_engine_and_loader_fuzz_under_sanitizers(fuzz_binary, tmp_path, seed):
     assert stats["engines"] > 100 and stats["steps"] > 1000 and stats["outputs"] > 20, r.stdout
     assert min(stats["prefill"], stats["paged"], stats["mixed"], stats["decode"]) > 0, r.stdout
     assert stats["injected"] > 20, r.stdout            # runner failures were injected and rolled back
+    assert stats["stateful"] > 100, r.stdout           # steps of runners with recurrent state: slots named, owned and reset
     assert "loader:" in r.stdout
 
 
 MUTANTS = {
+    # a recurrent-state slot stays on the free list after it was handed out: two live sequences share it
+    "state_slot_handed_out_twice": ("    free_state.pop_front();", "    // (mutant)"),
     # chunked prefill + prefix caching: a hit on a block whose K / V are not computed yet
     "hit_before_ready": ("(chunked && !blocks[id].ready))", "(false))"),
     # a shared block returned to the free list while another sequence still holds it
