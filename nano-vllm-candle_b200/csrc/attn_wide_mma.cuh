@@ -271,12 +271,12 @@ __global__ void __launch_bounds__(kWarps * 32) attn_wide_mma_kernel(const Args a
       }
       cp_async_commit();
     };
-    issue(0);
-    issue(1);
+#pragma unroll
+    for (int p = 0; p < kStages - 1; ++p) issue(p);
     for (int i = 0; i < n_tiles; ++i) {
-      cp_async_wait<1>();                 // tile i has landed (tile i + 1 may be in flight)
+      cp_async_wait<kStages - 2>();       // tile i has landed (later tiles may be in flight)
       __syncthreads();                    // ... for every thread's part of it; and every warp is done with tile i - 1,
-      issue(i + 2);                       // whose stage tile i + 2 takes
+      issue(i + kStages - 1);             // whose stage the newly issued tile takes
       const int tok0 = (tile0 + i) * kCtaTok;
       if (tok0 > kmax_w || tok0 + kCtaTok - 1 < kmin_w) continue;    // warp-uniform: nothing of this tile is visible to the warp
       const uint32_t st = ring + (i % kStages) * kTileBytes;
@@ -301,11 +301,11 @@ __global__ void __launch_bounds__(kWarps * 32) attn_wide_mma_kernel(const Args a
       if (i < n_tiles) load16(ring + (i % kStages) * kWarpStage, ring + (i % kStages) * kWarpStage + 16 * RBK, first + i * kCtaTok, kmax);
       cp_async_commit();
     };
-    issue(0);
-    issue(1);
+#pragma unroll
+    for (int p = 0; p < kStages - 1; ++p) issue(p);
     for (int i = 0; i < n_tiles; ++i) {
-      issue(i + 2);
-      cp_async_wait<2>();
+      issue(i + kStages - 1);
+      cp_async_wait<kStages - 1>();
       __syncwarp();
       const uint32_t st = ring + (i % kStages) * kWarpStage;
       const int tok0 = first + i * kCtaTok;

@@ -13,7 +13,7 @@
 //   linear up (+ relu^2) -> linear down (fp32)
 // The residual sum itself happens in the NEXT nvc_rms_norm_pair (or the final one), in fp32.
 //
-// Feature dimensions that a matrix product contracts or produces are padded to multiples of 64 in the weight and activation
+// Feature dimensions that a matrix product sums over or produces are padded to multiples of 64 in the weight and activation
 // buffers (zeros), so that the tcgen05 GEMMs (K % 64, N % 16) take every product of the bf16 mode; heads are NOT padded: q, the
 // caches and the attention kernels use the logical head sizes.
 #include <cmath>

@@ -89,10 +89,10 @@ R_WINDOW, R_DIM, R_RET_DIM = 256, 128, 64
 def ranilix_config(sz: dict) -> dict:
     H, W = sz["heads"], sz["width"]
     att = {"heads": H, "kv_heads": 8, "dim": R_DIM, "vdim": R_DIM, "scale": R_DIM ** -0.5, "mask": {"size": R_WINDOW},
-           "rot": {"dims": 64, "base": 500000.0}, "v_mix": True}
-    par = {"left": {"heads": H // 2, "kv_heads": 4, "dim": R_DIM, "vdim": R_DIM, "scale": R_DIM ** -0.5, "rot": {"dims": 64, "base": 1000000.0}},
+           "rot": {"dims": 64, "base": 10000.0}, "v_mix": True}
+    par = {"left": {"heads": H // 2, "kv_heads": 4, "dim": R_DIM, "vdim": R_DIM, "scale": R_DIM ** -0.5, "rot": {"dims": 64, "base": 10000.0}},
            "left_scale": 1.0,
-           "right": {"heads": H // 2, "dim": R_RET_DIM, "vdim": R_DIM, "rot": {"dims": R_RET_DIM, "base": 1000000.0},
+           "right": {"heads": H // 2, "dim": R_RET_DIM, "vdim": R_DIM, "rot": {"dims": R_RET_DIM, "base": 10000.0},
                      "decay": [1.0 - 2.0 ** (-5 - 5 * i / max(1, H // 2 - 1)) for i in range(H // 2)]},
            "right_scale": 1.0}
     mlp = {"kind": "dense", "ff": sz["ff"] * 3 // 2}
