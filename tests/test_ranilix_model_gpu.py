@@ -174,6 +174,24 @@ def test_a_request_left_out_of_steps_goes_on_later(rig):
     rig.check(pr, [[("a", 10), ("b", 5)], [("b", 20)], [("b", 1)], [("a", 1), ("b", 1)], [("b", 18)], [("a", 39)]])
 
 
+def test_steps_without_wanted_logits(rig):
+    """Steps that ask for no logits: single tokens go through the captured decode step (the state slots ride in its one
+    upload), portions through the mixed step; the next wanted position must not notice."""
+    V = rig.cfg["vocab"]
+    pa, pb = toks(60, V, 14), toks(45, V, 15)
+    a, b = rig.engine.open_request(), rig.engine.open_request()
+    rig.engine.step_forced([(a, pa[:20], []), (b, pb[:3], [])])
+    for i in range(30):
+        rig.engine.step_forced([(b, pb[3 + i:4 + i], []), (a, pa[20 + i:21 + i], [])])      # decode steps, nothing wanted
+    rig.engine.step_forced([(a, pa[50:59], [])])
+    lg = rig.engine.step_forced([(a, pa[59:], [0]), (b, pb[33:], [0, 11])])
+    wa, wb = rig.want(pa), rig.want(pb)
+    err = rig.rel_err(lg, np.stack([wa[59], wb[33], wb[44]]))
+    assert err.max() < rig.tol, err
+    rig.engine.close_request(a)
+    rig.engine.close_request(b)
+
+
 def test_pages_and_state_slots_are_freed_and_used_again(rig):
     """The pool holds 40 pages and four state slots; the requests below need 76 pages in total, at most 38 at a time, and
     every round takes state slots that the round before has left full."""
