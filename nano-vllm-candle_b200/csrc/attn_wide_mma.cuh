@@ -67,14 +67,15 @@ __device__ __forceinline__ void softmax_step(uint32_t stK, uint32_t stV, int tok
     const int r = (lane & 7) + ((lane >> 4) << 3);
     const int chi = (lane >> 3) & 1;
 #pragma unroll
-    for (int j = 0; j < NSUB; ++j) {
-      s[2 * j][0] = s[2 * j][1] = s[2 * j][2] = s[2 * j][3] = 0.f;
-      s[2 * j + 1][0] = s[2 * j + 1][1] = s[2 * j + 1][2] = s[2 * j + 1][3] = 0.f;
-      if (j < nsub) {
+    for (int j = 0; j < 2 * NSUB; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+    // k-steps outside, sub-tiles inside: consecutive MMAs go to different accumulators (no back-to-back dependent pairs)
 #pragma unroll
-        for (int ks = 0; ks < KS; ++ks) {
-          if (ks < ks_n) {
-            const int c = 2 * ks + chi;
+    for (int ks = 0; ks < KS; ++ks) {
+      if (ks < ks_n) {
+        const int c = 2 * ks + chi;
+#pragma unroll
+        for (int j = 0; j < NSUB; ++j) {
+          if (j < nsub) {
             uint32_t b0, b1, b2, b3;
             ldmatrix_x4(stK + (j * 16 + r) * RBK + ((c ^ (r & 7)) << 4), b0, b1, b2, b3);
             mma_bf16(s[2 * j], qa[ks], b0, b1);
