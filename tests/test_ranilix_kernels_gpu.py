@@ -243,10 +243,13 @@ def test_the_window_edge_is_where_it_belongs(ctx, ops, dt, H, G, d, vd, qlen, ba
 
 @pytest.mark.parametrize("dt", DTS)
 @pytest.mark.parametrize("where", [0, 1, 15, 16, 17, 500, 1023, 1024])
-def test_full_attention_finds_one_far_key(ctx, ops, dt, where):
+@pytest.mark.parametrize("qlens", [[3, 40], [1, 1]])
+def test_full_attention_finds_one_far_key(ctx, ops, dt, where, qlens):
+    """One key among 1 100 takes nearly all the weight of the last row - in a prompt portion and in a decode step (keys split over
+    warps) - wherever it lies: the first tokens, either side of a page border, far back."""
     n = 1100
-    got, want = run_attention(ctx, ops, dt, 4, 2, 32, 48, lens=[n, 40], qlens=[3, 40], bs=16, window=0, sink=False, gate=False, scale=1.0,
-                              seed=12, boost=(0, 2, where, 60.0))
+    got, want = run_attention(ctx, ops, dt, 4, 2, 32, 48, lens=[n, 40], qlens=qlens, bs=16, window=0, sink=False, gate=False, scale=1.0,
+                              seed=12, boost=(0, qlens[0] - 1, where, 60.0))
     assert torch.allclose(got, want, **tol(dt))
 
 
