@@ -110,7 +110,7 @@ int nvc_rms_norm_pair(nvc_ctx* ctx, const float* res_in, const float* a0, const 
   NVC_REQUIRE(ctx, ctx && (res_in || a0), NVC_EINVAL, "null pointer");
   NVC_REQUIRE(ctx, (w0 == nullptr) == (out0 == nullptr) && (w1 == nullptr) == (out1 == nullptr) && (w0 || !w1), NVC_EINVAL,
               "every norm needs its weight and its output; the second norm needs the first");
-  NVC_REQUIRE(ctx, N >= 0 && H > 0 && H <= 16384 && ld >= H && (!w0 || ldo >= H), NVC_EINVAL, "bad sizes");
+  NVC_REQUIRE(ctx, N >= 0 && H > 0 && H <= 12288 && ld >= H && (!w0 || ldo >= H), NVC_EINVAL, "bad sizes (rows of up to 12 288 numbers)");
   NVC_REQUIRE(ctx, !(rows && res_out), NVC_EINVAL, "a gathering call does not write the residual back");
   if (N == 0) return NVC_OK;
   const int threads = H >= 1024 ? 512 : (H >= 256 ? 256 : 128);
