@@ -261,6 +261,14 @@ int nvc_prefill_attn_paged(nvc_ctx* ctx, const nvc_bf16* q, int ldq, const nvc_b
                            int total_q_tokens, int max_seqlen_q, int nh, int kv, int hd, int block_size,
                            int num_blocks, float scale, nvc_bf16* out, void* stream);
 
+/* The same with a caller's output row stride ldo >= nh * hd (a multiple of 8; out 16-byte aligned): the heads' outputs may be the
+ * left part of wider rows (a mixer that concatenates the outputs of two halves in front of one output projection). */
+int nvc_prefill_attn_paged_ld(nvc_ctx* ctx, const nvc_bf16* q, int ldq, const nvc_bf16* k_cache,
+                              const nvc_bf16* v_cache, const int32_t* block_tables, int bt_stride,
+                              const int32_t* context_lens, const int32_t* cu_seqlens_q, int B,
+                              int total_q_tokens, int max_seqlen_q, int nh, int kv, int hd, int block_size,
+                              int num_blocks, float scale, nvc_bf16* out, int ldo, void* stream);
+
 /* K5. Decode: paged attention over block_tables (N2) with GQA head grouping.
  * q: [B, nh, hd] row stride ldq; caches [num_blocks, block_size, kv, hd];
  * block_tables: i32 [B, max_blocks] (-1 padded); context_lens: i32 [B] (tokens in the cache
@@ -396,7 +404,7 @@ int nvc_rotary_table_init_sync(nvc_ctx* ctx, float base, int dims, int max_pos, 
  * bias; per-head RMS norm of q and k (weights of `dim` numbers shared by the heads); rotary positions on the first rot_dims
  * numbers of every q / k head - pairs (2i, 2i + 1), or (i, i + rot_dims / 2) when rot_half - with (cos, sin) from rot_table at
  * positions[n]; k *= k_scale; value blending (NVC_BLEND_PROVIDE: v_first[n] = v, NVC_BLEND_MIX: v <- (1 - *lambda) v +
- * *lambda v_first[n]); q goes to q_out[n], k and v to row slot_mapping[n] of k_out / v_out (a paged cache; a negative slot
+ * *lambda v_first[n]); v *= v_scale; q goes to q_out[n], k and v to row slot_mapping[n] of k_out / v_out (a paged cache; a negative slot
  * skips the token) or to row n when slot_mapping == NULL. */
 enum { NVC_BLEND_NONE = 0, NVC_BLEND_PROVIDE = 1, NVC_BLEND_MIX = 2 };
 typedef struct nvc_qkv_prep {
@@ -412,6 +420,7 @@ typedef struct nvc_qkv_prep {
   void* k_out; void* v_out; int ldk, ldv;
   const int32_t* slot_mapping;
   int q_dtype, kv_dtype;
+  float v_scale;                          /* v *= v_scale on the way out (after blending); a mixer's constant weight can ride here */
 } nvc_qkv_prep;
 int nvc_qkv_prep_run(nvc_ctx* ctx, const nvc_qkv_prep* p, int N, void* stream);
 /* Grouped-query softmax attention over a paged cache with separate key and value widths:

@@ -86,6 +86,7 @@ def _declare(l: C.CDLL) -> None:
         "nvc_store_kvcache": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _vp],
         "nvc_prefill_attn_varlen": [_vp, _vp, _i, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _vp],
         "nvc_prefill_attn_paged": [_vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp],
+        "nvc_prefill_attn_paged_ld": [_vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _i, _vp],
         "nvc_paged_decode_attn": [_vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _f, _vp, _vp, _sz, _vp],
         "nvc_paged_decode_attn_static": [_vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _f, _vp, _vp],
         "nvc_silu_and_mul": [_vp, _vp, _vp, _i, _i, _vp],

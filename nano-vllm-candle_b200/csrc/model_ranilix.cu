@@ -50,6 +50,7 @@ struct RanilixBody : nvc_body_base {
   int Wp = 0, Vp = 0;
   int first_blend = -1;
   int state_slots = 0;
+  bool use_flash = true;               // tcgen05 paged-prefill kernel for long portions of plain causal attention with 128-wide heads
   std::vector<RLayerW> L;
   void *embed = nullptr, *head = nullptr;
   float* fw = nullptr;
@@ -102,6 +103,7 @@ struct RanilixBody : nvc_body_base {
     dt = r->dtype;
     esz = dt == NVC_DT_F32 ? 4 : 2;
     use_tc = dt == NVC_DT_BF16 && !(getenv("NVC_RANILIX_TC") && atoi(getenv("NVC_RANILIX_TC")) == 0);
+    use_flash = use_tc && !(getenv("NVC_RANILIX_FLASH") && atoi(getenv("NVC_RANILIX_FLASH")) == 0);
     Wp = pad64(cfg.width);
     Vp = pad64(cfg.vocab);
     first_blend = cfg.first_blend_layer();
@@ -271,6 +273,13 @@ struct RanilixBody : nvc_body_base {
     return NVC_OK;
   }
 
+  static constexpr int kFlashMinChunk = 64;
+  bool flash_portions(const nvc_runner* r, const nvc_step_shape& s, const nvc_softmax_attn_spec& a, bool is_attention_layer) const {
+    const int bs = r->opt.kvcache_block_size;
+    return use_flash && !is_attention_layer && a.window == 0 && a.dim == 128 && a.vdim == 128 && !s.decode && s.num_decode < s.B &&
+           s.max_chunk >= kFlashMinChunk && (bs == 16 || bs == 32 || bs == 64 || bs % 128 == 0);
+  }
+
   // bias / norms / rotary / blending / cache store of a softmax-attention mixer, then the attention itself into ao[:, :heads * vdim]
   int softmax_mixer(nvc_runner* r, const nvc_step_shape& s, int li, bool is_attention_layer, float out_scale) {
     nvc_ctx* ctx = r->ctx;
@@ -286,6 +295,7 @@ struct RanilixBody : nvc_body_base {
     p.eps = cfg.eps;
     p.rot_dims = a.rot.dims; p.rot_half = 0; p.rot_table = w.rot; p.positions = r->d_pos;
     p.k_scale = 1.f;
+    p.v_scale = out_scale;             // the mixer's constant weight rides on the cached values: no attention kernel needs to know it
     p.blend = !a.blend_values ? NVC_BLEND_NONE : (li == first_blend ? NVC_BLEND_PROVIDE : NVC_BLEND_MIX);
     p.lambda = w.lambda; p.v_first = v_first; p.ldvf = blend_w;
     p.q_out = q; p.ldq = a.heads * a.dim;
@@ -302,10 +312,26 @@ struct RanilixBody : nvc_body_base {
     sp.sink = is_attention_layer ? w.sink : nullptr;
     sp.gate = is_attention_layer ? proj + w.g_off : nullptr;
     sp.ldg = w.np;
-    sp.out_scale = out_scale;
-    rc = nvc_attn_paged_wide(ctx, q, p.ldq, w.k_cache, p.ldk, w.v_cache, p.ldv, r->d_bt, r->max_blocks_cap, r->d_ctx,
-                             s.decode ? nullptr : r->d_cu, s.B, s.N, s.decode ? 1 : s.max_seqlen, r->opt.kvcache_block_size, &sp, ao, w.ow, dt,
-                             r->stream);
+    sp.out_scale = 1.f;
+    const int bs = r->opt.kvcache_block_size, cap = r->max_blocks_cap;
+    if (flash_portions(r, s, a, is_attention_layer)) {
+      // Plain causal attention with 128-wide keys and values is what the tcgen05 paged-prefill kernel of the Qwen3 family
+      // computes: long prompt portions go there (it writes the left part of the output projection's input through its row
+      // stride); the one-token sequences of a mixed step come first in the batch and keep the decode path of the wide kernel.
+      const int nd = s.num_decode;
+      const nvc_bf16* qb = reinterpret_cast<const nvc_bf16*>(q);
+      nvc_bf16* ob = reinterpret_cast<nvc_bf16*>(ao);
+      if (nd > 0 && (rc = nvc_attn_paged_wide(ctx, q, p.ldq, w.k_cache, p.ldk, w.v_cache, p.ldv, r->d_bt, cap, r->d_ctx, nullptr, nd, nd, 1, bs,
+                                              &sp, ao, w.ow, dt, r->stream)))
+        return rc;
+      rc = nvc_prefill_attn_paged_ld(ctx, qb + (size_t)nd * p.ldq, p.ldq, reinterpret_cast<const nvc_bf16*>(w.k_cache),
+                                     reinterpret_cast<const nvc_bf16*>(w.v_cache), r->d_bt + (size_t)nd * cap, cap, r->d_ctx + nd,
+                                     nd ? r->d_cu2 : r->d_cu, s.B - nd, s.N - nd, s.max_chunk, a.heads, a.kv_heads, a.dim, bs,
+                                     r->opt.num_kvcache_blocks, a.scale, ob + (size_t)nd * w.ow, w.ow, r->stream);
+    } else {
+      rc = nvc_attn_paged_wide(ctx, q, p.ldq, w.k_cache, p.ldk, w.v_cache, p.ldv, r->d_bt, cap, r->d_ctx, s.decode ? nullptr : r->d_cu, s.B,
+                               s.N, s.decode ? 1 : s.max_seqlen, bs, &sp, ao, w.ow, dt, r->stream);
+    }
     mark(r, "attention");
     return rc;
   }
@@ -322,6 +348,7 @@ struct RanilixBody : nvc_body_base {
     p.eps = cfg.eps;
     p.rot_dims = rt.rot.dims; p.rot_half = 1; p.rot_table = w.rrot; p.positions = r->d_pos;
     p.k_scale = 1.0f / sqrtf((float)rt.dim);
+    p.v_scale = 1.f;
     p.blend = NVC_BLEND_NONE;
     p.q_out = rq; p.ldq = qw;
     p.k_out = rk; p.v_out = rv; p.ldk = qw; p.ldv = vw;

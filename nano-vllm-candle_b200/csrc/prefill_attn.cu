@@ -64,13 +64,13 @@ int make_tma_heads(nvc_ctx* ctx, CUtensorMap* map, const void* base, int heads, 
 // persistent grid of the second-generation kernel: two CTAs per SM, or one CTA per work item when there are fewer
 template <bool kPaged>
 cudaError_t launch_v2(nvc_ctx* ctx, int QT, int nh, int kv, int B, cudaStream_t st, const CUtensorMap& tq, const CUtensorMap& tk,
-                      const CUtensorMap& tv, const int32_t* cu_seqlens, float scale_log2e, nvc_bf16* out, const PagedKV& pk) {
+                      const CUtensorMap& tv, const int32_t* cu_seqlens, float scale_log2e, nvc_bf16* out, int ldo, const PagedKV& pk) {
   const long long items = (long long)QT * nh * B;
   if (items > 0x7fffffffLL) return cudaErrorInvalidValue;
   const int grid = (int)(items < 2LL * ctx->num_sms ? items : 2LL * ctx->num_sms);
   v2::Sched sc{v2::make_fastdiv(nh * B), v2::make_fastdiv(nh), v2::make_fastdiv(nh / kv), QT, (int)items};
   return nvc_launch(ctx, v2::prefill_attn_v2_kernel<kPaged>, dim3(grid), dim3(v2::kThreads), v2::kSmemBytes, st, tq, tk, tv,
-                    cu_seqlens, sc, scale_log2e, out, pk);
+                    cu_seqlens, sc, scale_log2e, out, ldo, pk);
 }
 
 }  // namespace
@@ -104,7 +104,7 @@ extern "C" int nvc_prefill_attn_varlen(nvc_ctx* ctx, const nvc_bf16* q, int ldq,
   if (rc) return rc;
   const int QT = (max_seqlen + 127) / 128;
   NVC_CUDA_CHECK(ctx, launch_v2<false>(ctx, QT, nh, kv, B, nvc_stream(stream), tq, tk, tv, cu_seqlens,
-                                       scale * 1.4426950408889634f, out, PagedKV{}));
+                                       scale * 1.4426950408889634f, out, nh * hd, PagedKV{}));
   NVC_CUDA_CHECK(ctx, cudaGetLastError());
   ctx->launches++;
   return NVC_OK;
@@ -115,6 +115,17 @@ extern "C" int nvc_prefill_attn_paged(nvc_ctx* ctx, const nvc_bf16* q, int ldq, 
                                       const int32_t* context_lens, const int32_t* cu_seqlens_q, int B,
                                       int total_q_tokens, int max_seqlen_q, int nh, int kv, int hd, int block_size,
                                       int num_blocks, float scale, nvc_bf16* out, void* stream) {
+  return nvc_prefill_attn_paged_ld(ctx, q, ldq, k_cache, v_cache, block_tables, bt_stride, context_lens, cu_seqlens_q, B, total_q_tokens,
+                                   max_seqlen_q, nh, kv, hd, block_size, num_blocks, scale, out, nh * hd, stream);
+}
+
+extern "C" int nvc_prefill_attn_paged_ld(nvc_ctx* ctx, const nvc_bf16* q, int ldq, const nvc_bf16* k_cache,
+                                         const nvc_bf16* v_cache, const int32_t* block_tables, int bt_stride,
+                                         const int32_t* context_lens, const int32_t* cu_seqlens_q, int B,
+                                         int total_q_tokens, int max_seqlen_q, int nh, int kv, int hd, int block_size,
+                                         int num_blocks, float scale, nvc_bf16* out, int ldo, void* stream) {
+  NVC_REQUIRE(ctx, ctx && ldo >= nh * hd && ldo % 8 == 0 && ((uintptr_t)out % 16) == 0, NVC_ESHAPE,
+              "output rows must cover the heads, with a stride that is a multiple of 8 and a 16-byte aligned start");
   NVC_REQUIRE(ctx, ctx && q && k_cache && v_cache && block_tables && context_lens && cu_seqlens_q && out, NVC_EINVAL,
               "null pointer");
   NVC_REQUIRE(ctx, B >= 0 && total_q_tokens >= 0 && max_seqlen_q >= 0 && nh > 0 && kv > 0 && bt_stride > 0 &&
@@ -139,7 +150,7 @@ extern "C" int nvc_prefill_attn_paged(nvc_ctx* ctx, const nvc_bf16* q, int ldq, 
   PagedKV pk{block_tables, context_lens, bt_stride, block_size, box_rows};
   const int QT = (max_seqlen_q + 127) / 128;
   NVC_CUDA_CHECK(ctx, launch_v2<true>(ctx, QT, nh, kv, B, nvc_stream(stream), tq, tk, tv, cu_seqlens_q,
-                                      scale * 1.4426950408889634f, out, pk));
+                                      scale * 1.4426950408889634f, out, ldo, pk));
   NVC_CUDA_CHECK(ctx, cudaGetLastError());
   ctx->launches++;
   return NVC_OK;

@@ -79,7 +79,7 @@ template <bool kPaged>
 __global__ void __launch_bounds__(192, 2)
 prefill_attn_v2_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                        const __grid_constant__ CUtensorMap tma_v, const int32_t* __restrict__ cu_seqlens, const Sched sc,
-                       float scale_log2e, nvc_bf16* __restrict__ out, const PagedKV pk) {
+                       float scale_log2e, nvc_bf16* __restrict__ out, int ldo, const PagedKV pk) {
   pdl_trigger();
   const int num_items = sc.num_items, nh = sc.nh.d;
   extern __shared__ __align__(1024) uint8_t smem_v2[];
@@ -389,7 +389,7 @@ prefill_attn_v2_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
       ptx::tcgen05_fence_after();
       const float inv = 1.0f / l;
       // this warp's 32 rows x 128 head dims leave through its staging buffer: 8 lanes per row, 128 contiguous bytes each
-      RowStage st = make_row_stage(gen + kOffStage + quad * 4096, out, 0, NVC_EPI_NONE, (int64_t)nh * 128,
+      RowStage st = make_row_stage(gen + kOffStage + quad * 4096, out, 0, NVC_EPI_NONE, (int64_t)ldo,
                                    ge.seq_start + x.qt * 128 + quad * 32, ge.seq_start + ge.seq_len, x.h * 128, 128, nh * 128);
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {

@@ -6,6 +6,7 @@
 //                                            angles from a table of (cos, sin) per position
 //   k *= k_scale                             (after the rotation)
 //   value blending                           v <- (1 - lambda) v + lambda v_first, or v_first <- v in the layer that provides it
+//   v *= v_scale                             (a constant weight of the mixer, so that every attention kernel can leave it out)
 //   stores                                   q to its buffer; k and v to rows of a paged cache (slot mapping) or to plain rows
 // One warp per (token, head) of q, k or v; a head is staged in shared memory so that any pairing reads its partner.
 #include "typed.cuh"
@@ -41,6 +42,7 @@ __global__ void qkv_prep_kernel(const PrepArgs a) {
       float v = in[col + j] + (p.bias ? __ldg(p.bias + col + j) : 0.f);
       if (p.blend == NVC_BLEND_PROVIDE) p.v_first[(int64_t)n * p.ldvf + h * p.vdim + j] = v;
       else if (p.blend == NVC_BLEND_MIX) v = (1.0f - lam) * v + lam * p.v_first[(int64_t)n * p.ldvf + h * p.vdim + j];
+      v *= p.v_scale;
       if (orow >= 0) st_f(reinterpret_cast<TKV*>(p.v_out) + orow * p.ldv + h * p.vdim + j, v);
     }
     return;

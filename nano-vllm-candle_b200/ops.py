@@ -257,6 +257,16 @@ class Context:
                  "nvc_prefill_attn_paged")
         return out
 
+    def prefill_attn_paged_ld(self, q, k_cache, v_cache, block_tables, context_lens, cu_seqlens_q, max_seqlen_q,
+                              nh, kv, hd, block_size, scale, out):
+        """The same into the left nh * hd columns of wider rows: out [N, >= nh * hd], any row stride that is a multiple of 8."""
+        N, B = q.shape[0], cu_seqlens_q.numel() - 1
+        self._ck(self.l.nvc_prefill_attn_paged_ld(self.h, _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
+                                                  block_tables.shape[1], _ptr(context_lens), _ptr(cu_seqlens_q), B, N, max_seqlen_q, nh,
+                                                  kv, hd, block_size, k_cache.shape[0], float(scale), _ptr(out), out.stride(0), _stream()),
+                 "nvc_prefill_attn_paged_ld")
+        return out
+
     def paged_decode_attn(self, q, k_cache, v_cache, block_tables, context_lens, nh, kv, hd, block_size, scale, out=None):
         _req(q, BF16, "q"); _req(block_tables, torch.int32, "block_tables"); _req(context_lens, torch.int32, "context_lens")
         B = q.shape[0]
@@ -486,7 +496,7 @@ class QkvPrepC(C.Structure):
                 ("k_norm", C.c_void_p), ("eps", C.c_float), ("rot_dims", C.c_int), ("rot_half", C.c_int), ("rot_table", C.c_void_p),
                 ("positions", C.c_void_p), ("k_scale", C.c_float), ("blend", C.c_int), ("lambda_", C.c_void_p), ("v_first", C.c_void_p),
                 ("ldvf", C.c_int), ("q_out", C.c_void_p), ("ldq", C.c_int), ("k_out", C.c_void_p), ("v_out", C.c_void_p), ("ldk", C.c_int),
-                ("ldv", C.c_int), ("slot_mapping", C.c_void_p), ("q_dtype", C.c_int), ("kv_dtype", C.c_int)]
+                ("ldv", C.c_int), ("slot_mapping", C.c_void_p), ("q_dtype", C.c_int), ("kv_dtype", C.c_int), ("v_scale", C.c_float)]
 
 
 class AttnSpecC(C.Structure):
@@ -536,12 +546,12 @@ def rotary_table(ctx, base: float, dims: int, max_pos: int, device="cuda:0"):
 
 def qkv_prep(ctx, x, q_off, k_off, v_off, q_heads, kv_heads, dim, vdim, q_out, k_out, v_out, *, bias=None, q_norm=None, k_norm=None,
              eps=1e-5, rot_dims=0, rot_half=False, rot_table=None, positions=None, k_scale=1.0, blend=0, lam=None, v_first=None,
-             slot_mapping=None):
+             slot_mapping=None, v_scale=1.0):
     """x: fp32 [N, ld] rows of a fused projection; q_out [N, q_heads * dim]; k_out / v_out: cache rows (slot_mapping) or [N, ...]."""
     p = QkvPrepC(_a(x), x.stride(0), _a(bias), q_off, k_off, v_off, q_heads, kv_heads, dim, vdim, _a(q_norm), _a(k_norm), eps, rot_dims,
                  1 if rot_half else 0, _a(rot_table), _a(positions), k_scale, blend, _a(lam), _a(v_first),
                  v_first.stride(0) if v_first is not None else 0, _a(q_out), q_out.stride(0), _a(k_out), _a(v_out), k_out.stride(0),
-                 v_out.stride(0), _a(slot_mapping), _dt(q_out), _dt(k_out))
+                 v_out.stride(0), _a(slot_mapping), _dt(q_out), _dt(k_out), v_scale)
     check(ctx.l.nvc_qkv_prep_run(ctx.h, C.byref(p), x.shape[0], _stream()), "nvc_qkv_prep_run", ctx.h)
 
 

@@ -135,6 +135,8 @@ def test_value_blending_provider_and_user(ctx, ops, dt):
     assert torch.allclose(outs[2].float().cpu(), v1, **tol(dt))
     ops.qkv_prep(ctx, x2.to(DEV), 0, H * d, H * d + G * d, H, G, d, vd, *outs, blend=2, lam=lam.to(DEV), v_first=vf)
     assert torch.allclose(outs[2].float().cpu(), 0.7 * x2[:, -G * vd:] + 0.3 * v1, **tol(dt))
+    ops.qkv_prep(ctx, x2.to(DEV), 0, H * d, H * d + G * d, H, G, d, vd, *outs, blend=2, lam=lam.to(DEV), v_first=vf, v_scale=1.5)
+    assert torch.allclose(outs[2].float().cpu(), 1.5 * (0.7 * x2[:, -G * vd:] + 0.3 * v1), **tol(dt))      # the factor comes last
     assert torch.allclose(vf.cpu(), v1, rtol=1e-6, atol=1e-6)            # a user does not change what the provider left
 
 
@@ -268,6 +270,25 @@ def test_a_large_sink_takes_the_weight_and_a_small_one_does_not(ctx, ops, dt):
         assert torch.allclose(got, want, **tol(dt))
         big = 0 if s0 > 0 else 1
         assert got[0, big * vd:(big + 1) * vd].abs().max() < 1e-6 and got[0, (1 - big) * vd:(2 - big) * vd].abs().max() > 1e-2
+
+
+def test_paged_prefill_kernel_writes_into_wider_rows(ctx, ops):
+    """The tcgen05 paged-prefill kernel with a caller's output row stride: its heads land in the left columns of wider rows and
+    the columns to their right stay as they were."""
+    g = torch.Generator().manual_seed(16)
+    H, G, d, bs, lens, qlens = 4, 2, 128, 16, [200, 90], [130, 90]
+    ks = [torch.randn(n, G, d, generator=g).bfloat16().float() for n in lens]
+    vs = [torch.randn(n, G, d, generator=g).bfloat16().float() for n in lens]
+    qs = [torch.randn(m, H, d, generator=g).bfloat16().float() for m in qlens]
+    want = torch.cat([R.softmax_attention(qs[b], ks[b], vs[b], 0.09, torch.arange(lens[b] - qlens[b], lens[b])) for b in range(2)])
+    nblocks = sum((n + bs - 1) // bs for n in lens) + 2
+    kc, vc, tables = paged([k.reshape(k.shape[0], -1) for k in ks], [v.reshape(v.shape[0], -1) for v in vs], bs, nblocks, g)
+    rows = sum(qlens)
+    out = torch.full((rows, H * d + 72), 7.0, dtype=torch.bfloat16, device=DEV)
+    ctx.prefill_attn_paged_ld(torch.cat(qs).reshape(rows, H * d).bfloat16().to(DEV), kc.view(nblocks, bs, G, d).bfloat16().to(DEV),
+                              vc.view(nblocks, bs, G, d).bfloat16().to(DEV), i32(tables), i32(lens), i32([0, 130, 220]), 130, H, G, d, bs, 0.09, out)
+    assert torch.allclose(out[:, :H * d].float().cpu(), want, rtol=2e-2, atol=2e-2)
+    assert (out[:, H * d:].float() == 7.0).all()
 
 
 # ---------------------------------------------------------------------------------------------------------------- retention

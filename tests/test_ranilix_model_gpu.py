@@ -45,6 +45,16 @@ def cfg_c():
     ])
 
 
+def cfg_d():
+    """Parallel layers whose causal half has keys and values of 128 numbers: in the bf16 mode its long prompt portions run on the
+    tcgen05 paged-prefill kernel; one of them shares key heads between query heads, and both weights differ from 1."""
+    return R.make_config(vocab=180, width=192, layers=[
+        R.with_mlp(R.parallel_cfg(2, 1, 128, 128, rot_dims=64, scale=0.09, left_scale=1.4, r_heads=2, r_dim=16, r_vdim=32, r_rot_dims=8, decay=(0.9, 0.99), right_scale=0.7), 128),
+        R.with_mlp(R.attention_cfg(2, 2, 32, 32, window=70, rot_dims=16, scale=0.2), None),
+        R.with_mlp(R.parallel_cfg(3, 3, 128, 128, rot_dims=0, scale=0.08, left_scale=0.6, r_heads=1, r_dim=24, r_vdim=40, r_rot_dims=24, decay=(0.995,), right_scale=1.2), 96),
+    ])
+
+
 class Rig:
     def __init__(self, cfg, dtype, blocks=40, seed=0, chunked=True, seqs=4, weights=None):
         self.eng = importlib.import_module("nano-vllm-candle_b200.engine")
@@ -246,6 +256,27 @@ def test_head_sizes_of_the_tensor_pipe_attention(dtype):
         r.check(pr, sched)
         r.check({"w": toks(200, V, 64)}, [[("w", 9)], [("w", 191)]])
         r.check({"w": toks(200, V, 64)}, [[("w", 140)]] + [[("w", 1)]] * 60)
+    finally:
+        r.close()
+
+
+@pytest.mark.parametrize("flash", ["1", "0"])
+def test_long_portions_of_the_causal_half_beside_decoded_tokens(monkeypatch, flash):
+    """Portions of 64 tokens and more - whole prompts, behind a cached prefix that ends inside a page, beside one-token
+    sequences of the same step - with the tcgen05 route of the causal half on and off: which kernel computed a position depends
+    on the schedule, so both must agree with the oracle alike."""
+    monkeypatch.setenv("NVC_RANILIX_FLASH", flash)
+    r = Rig(cfg_d(), "bfloat16", blocks=48, seed=12)
+    try:
+        V = r.cfg["vocab"]
+        pr = {"a": toks(333, V, 60), "b": toks(131, V, 61), "c": toks(70, V, 62), "d": toks(5, V, 63)}
+        sched = [[("a", 129), ("d", 1)], [("d", 1), ("a", 64), ("b", 77)], [("d", 1), ("a", 1), ("b", 3), ("c", 70)],
+                 [("d", 1), ("b", 51), ("a", 139)], [("d", 1)]]
+        assert all(sum(n for s in sched for k, n in s if k == name) == len(p) for name, p in pr.items())
+        r.check(pr, sched)
+        r.check({"w": toks(200, V, 64)}, [[("w", 200)]])
+        r.check({"w": toks(200, V, 64)}, [[("w", 9)], [("w", 191)]])
+        r.check({"w": toks(200, V, 64)}, [[("w", 150)]] + [[("w", 1)]] * 50)
     finally:
         r.close()
 
